@@ -1,0 +1,224 @@
+/*
+ * sparse_b200 — C ABI of the B200 (sm_100a) MoE-layer hot path.
+ *
+ * The reference project is pure Python and has no foreign-function interface;
+ * every entry point below replaces a span of Python/ATen calls inside
+ * `DistributedSparseMoeBlock` (file utils/eval_core.py of the reference), named
+ * in the comment above it.  A host program binds these symbols with ctypes
+ * (or cgo/JNI/N-API, the signatures are plain C) and passes raw device
+ * pointers, sizes and a CUDA stream.
+ *
+ * Conventions
+ *   - every function returns 0 on success and a negative SB_E_* code on
+ *     failure; `sb_last_error_string()` describes the last failure of the
+ *     calling thread;
+ *   - nothing here allocates or frees device memory, synchronises the host
+ *     with the device, or keeps a pointer after the call returns, unless the
+ *     function's comment says otherwise;
+ *   - `stream` is a `cudaStream_t` passed as `void *` (NULL = legacy default);
+ *   - activations and weights are bf16, row-major, nn.Linear layout
+ *     ([out_features, in_features]); indices are int32;
+ *   - all device pointers must be 16-byte aligned; matrices handed to the
+ *     grouped GEMM must be 128-byte aligned.
+ */
+#ifndef SPARSE_B200_H_
+#define SPARSE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_OK                 0
+#define SB_E_INVALID_ARG     -1
+#define SB_E_WORKSPACE       -2   /* workspace too small */
+#define SB_E_CUDA            -3   /* a CUDA runtime/driver call failed */
+#define SB_E_UNSUPPORTED     -4   /* shape outside what the kernels cover */
+#define SB_E_DEVICE_TIMEOUT  -5   /* a bounded device-side wait gave up */
+
+#define SB_DTYPE_BF16 0
+#define SB_DTYPE_F32  1
+
+#define SB_COPY_HOST_TO_DEVICE 0   /* pinned host -> cache slot */
+#define SB_COPY_PEER_TO_DEVICE 1   /* peer GPU    -> cache slot */
+#define SB_COPY_DEVICE_LOCAL   2
+
+/* Rows per GEMM tile; `sb_permute` cuts every expert segment into tiles of
+ * this many rows and the grouped GEMM consumes that table. */
+#define SB_TILE_M 128
+
+/* ABI version of this header (bumped on any signature change). */
+int32_t sb_abi_version(void);
+
+/* Text for the calling thread's last non-zero status. */
+const char *sb_last_error_string(void);
+
+/* Number of SMs of the current device (grid sizing on the host side). */
+int32_t sb_device_sm_count(void);
+
+/*
+ * Router: logits = x . Wg^T (+ bias) rounded to the model dtype, softmax in
+ * fp32, top-k (larger probability first, then smaller expert id), optional
+ * renormalisation, weights cast to the model dtype.  Optionally also the
+ * shared expert's scalar gate sigmoid(x . wsg) in the model dtype.
+ * Replaces `_routing_router` (utils/eval_core.py:9519-9520, 9591-9595) and the
+ * gate half of `_shared_expert_forward` (utils/eval_core.py:9461-9462).
+ *
+ *   x            [T,H]   model dtype (bf16 or f32 per `dtype`)
+ *   wg           [E,H]   same dtype
+ *   bias         [E]     f32 values already rounded to the model dtype, or NULL
+ *   w_shared_gate[H]     same dtype as x, or NULL
+ *   out_idx      [T,K]   int32
+ *   out_w        [T,K]   model dtype
+ *   fp32_logits  0: logits are rounded to the model dtype before the softmax
+ *                (Qwen-MoE gate, an nn.Linear in the model dtype);
+ *                1: logits stay fp32 (DeepSeek-V2 gate, which casts its inputs
+ *                to fp32; that gate is third-party remote code the reference
+ *                only calls, utils/eval_core.py:9503-9517)
+ *   out_logits   [T,E]   model dtype (f32 if fp32_logits), or NULL
+ *   out_shared_scale [T] model dtype, or NULL (required iff w_shared_gate)
+ * Limits: H % 8 == 0, 1 <= K <= 8, K <= E <= 256.
+ */
+int32_t sb_router_topk(const void *x, const void *wg, const float *bias,
+                       const void *w_shared_gate, int32_t T, int32_t H, int32_t E,
+                       int32_t K, int32_t renorm, int32_t dtype, int32_t fp32_logits,
+                       int32_t *out_idx, void *out_w, void *out_logits,
+                       void *out_shared_scale, void *stream);
+
+/* Same stage, but starting from given model-dtype logits [T,E] (softmax +
+ * top-k only).  Used to check the tie rule in isolation. */
+int32_t sb_softmax_topk(const void *logits, int32_t T, int32_t E, int32_t K,
+                        int32_t renorm, int32_t dtype, int32_t *out_idx,
+                        void *out_w, void *stream);
+
+/* Bytes of scratch `sb_permute` needs for `n_items` items over E experts. */
+size_t sb_permute_workspace_bytes(int32_t n_items, int32_t E);
+
+/* Number of int32 the tile table needs for `n_items` items over E experts. */
+size_t sb_tile_table_ints(int32_t n_items, int32_t E);
+
+/*
+ * Expert-sorted permutation: stable counting sort of the flat items by expert
+ * id, gather of the activation rows into that order, and the row-tile table
+ * the grouped GEMM walks.  Item i reads source row i / items_per_row.
+ * Replaces the expand/argsort/gather/bincount sequence of the reference
+ * (utils/eval_core.py:14873-14882) and the local re-sort by expert
+ * (utils/eval_core.py:13240-13253); the EP=1 loop of `_experts_world1_exact`
+ * (utils/eval_core.py:14690-14700) needs the same grouping.
+ *
+ *   x              [n_items/items_per_row, H] bf16
+ *   item_expert    [n_items] int32 in [0,E); a negative id drops the item
+ *   item_scale     [n_items] bf16 route weight per item, or NULL
+ *   ws             scratch of sb_permute_workspace_bytes()
+ *   out_rows       [n_items,H] bf16, rows in expert-sorted order
+ *   expert_offsets [E+1] int32
+ *   slot_of_item   [n_items] int32 (-1 for dropped items)
+ *   item_of_slot   [n_items] int32
+ *   slot_scale     [n_items] bf16 = item_scale[item_of_slot], or NULL
+ *   tile_table     [sb_tile_table_ints()] int32: [0] = number of row tiles,
+ *                  then from int 4 on one (expert, row_begin, row_end, 0)
+ *                  quadruple per tile, tiles of one expert adjacent.
+ */
+int32_t sb_permute(const void *x, const int32_t *item_expert, const void *item_scale,
+                   int32_t n_items, int32_t items_per_row, int32_t H, int32_t E,
+                   void *ws, size_t ws_bytes, void *out_rows, int32_t *expert_offsets,
+                   int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale,
+                   int32_t *tile_table, void *stream);
+
+/*
+ * Grouped SwiGLU expert MLP on the tensor cores (tcgen05, TMEM accumulators,
+ * TMA-fed): for every row tile of `tile_table`
+ *     h   = bf16( bf16(silu(bf16(x.Wg^T))) * bf16(x.Wu^T) )
+ *     out = bf16( bf16(h.Wd^T) * row_scale )
+ * with the same rounding points as the reference's three `F.linear` calls and
+ * the `* cur_w` that follows (utils/eval_core.py:11787-11790, 11765).
+ *
+ *   rows          [R_cap,H] bf16, expert-sorted (out_rows of sb_permute)
+ *   tile_table    as written by sb_permute; NULL = one dense group of
+ *                 `dense_rows` rows using weight slot 0 (shared expert)
+ *   w13           [S, 2*I, H] bf16 weight slab: per slot gate rows then up rows
+ *   w2            [S, H, I]   bf16 weight slab
+ *   slot_of_expert[E] int32 expert id -> weight slot, or NULL for identity
+ *   row_scale     [R_cap] bf16 per-row factor, or NULL for none
+ *   hbuf          [R_cap, I] bf16 scratch for the intermediate
+ *   out           [R_cap, H] bf16
+ *   status        device int32; set non-zero if a bounded wait gave up
+ * Limits: H % 64 == 0, I % 64 == 0, H,I >= 64.
+ */
+int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
+                          int32_t dense_rows, const void *w13, const void *w2,
+                          const int32_t *slot_of_expert, const void *row_scale,
+                          int32_t R_cap, int32_t H, int32_t I, int32_t S,
+                          void *hbuf, void *out, int32_t *status, void *stream);
+
+/*
+ * Un-permute and combine: for each token add its K expert rows in ascending
+ * expert id, every add rounding to bf16, then add the shared expert's row.
+ * Replaces the unsort + `combine_expert_outputs` + final add
+ * (utils/eval_core.py:15058-15060, 523-538, 16547).
+ *
+ *   rows_out     [n_items,H] bf16 expert-sorted rows (already route-weighted)
+ *   slot_of_item [T*K] int32 (-1 = contributes nothing)
+ *   idx          [T,K] int32 expert ids (ordering key)
+ *   shared_out   [T,H] bf16 or NULL
+ *   out          [T,H] bf16
+ * Limits: H % 8 == 0, K <= 8.
+ */
+int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item,
+                   const int32_t *idx, const void *shared_out, int32_t T, int32_t H,
+                   int32_t K, void *out, void *stream);
+
+/*
+ * Asynchronous copy of one expert payload into a preallocated cache slot on
+ * `stream` (pinned host memory, a peer GPU, or this GPU).  Callable from a
+ * second host thread while kernels are launched on other streams; `device` is
+ * made current for the call.  Replaces the `.to(device, non_blocking=True)`
+ * weight copies (utils/eval_core.py:11379-11380, 11427-11429, 9975-9982,
+ * 11626-11633; utils/rs_overlap.py:245-248).
+ */
+int32_t sb_slot_copy_async(void *dst_slot, const void *src, size_t bytes,
+                           int32_t kind, int32_t device, void *stream);
+
+/* Everything one single-GPU layer pass needs; all pointers are device
+ * pointers owned by the caller. */
+typedef struct sb_moe_layer {
+  int32_t T, H, E, K, I, I_shared, renorm, n_slots;
+  int32_t router_fp32_logits;    /* see sb_router_topk */
+  int32_t reserved_;
+  const void *x;                 /* [T,H] bf16 */
+  const void *router_w;          /* [E,H] bf16 */
+  const float *router_bias;      /* [E] or NULL */
+  const void *shared_gate_w;     /* [H] bf16 or NULL */
+  const void *w13, *w2;          /* routed slabs [S,2I,H], [S,H,I] */
+  const int32_t *slot_of_expert; /* [E] or NULL */
+  const void *shared_w13, *shared_w2; /* [1,2Is,H], [1,H,Is] or NULL */
+  /* outputs */
+  void *out;                     /* [T,H] bf16 */
+  void *logits;                  /* [T,E] bf16 (f32 if router_fp32_logits) or NULL */
+  int32_t *topk_idx;             /* [T,K] */
+  void *topk_w;                  /* [T,K] bf16 */
+  /* scratch, sized for T*K items */
+  void *ws; size_t ws_bytes;     /* sb_moe_layer_workspace_bytes() */
+} sb_moe_layer;
+
+size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K,
+                                    int32_t I, int32_t I_shared);
+
+/*
+ * One whole single-GPU layer pass: router -> permute -> routed grouped SwiGLU
+ * -> shared expert -> combine, all on `stream`, without a host sync.
+ * Replaces `DistributedSparseMoeBlock.forward` at world=1
+ * (utils/eval_core.py:16418-16563 with 14690-14721 and 9455-9463).
+ * `status` is a device int32 (may be NULL) as in sb_grouped_swiglu.
+ */
+int32_t sb_moe_layer_forward(const sb_moe_layer *layer, int32_t *status, void *stream);
+
+/* Number of kernels the last sb_moe_layer_forward of this thread launched. */
+int32_t sb_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSE_B200_H_ */

@@ -1,0 +1,78 @@
+"""ctypes binding of libsparse_b200.so (the C ABI in include/sparse_b200.h).
+
+There is no fallback: if the library is missing the import of this module
+raises, and every op raises `RuntimeError` with the library's own message on a
+non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Tuple
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libsparse_b200.so")
+
+SB_OK = 0
+SB_DTYPE_BF16 = 0
+SB_DTYPE_F32 = 1
+SB_COPY_HOST_TO_DEVICE = 0
+SB_COPY_PEER_TO_DEVICE = 1
+SB_COPY_DEVICE_LOCAL = 2
+SB_TILE_M = 128
+
+i32, vp, sz = C.c_int32, C.c_void_p, C.c_size_t
+
+
+class MoeLayer(C.Structure):
+    """Mirror of `struct sb_moe_layer`."""
+    _fields_ = [
+        ("T", i32), ("H", i32), ("E", i32), ("K", i32), ("I", i32), ("I_shared", i32),
+        ("renorm", i32), ("n_slots", i32), ("router_fp32_logits", i32), ("reserved_", i32),
+        ("x", vp), ("router_w", vp), ("router_bias", vp), ("shared_gate_w", vp),
+        ("w13", vp), ("w2", vp), ("slot_of_expert", vp),
+        ("shared_w13", vp), ("shared_w2", vp),
+        ("out", vp), ("logits", vp), ("topk_idx", vp), ("topk_w", vp),
+        ("ws", vp), ("ws_bytes", sz),
+    ]
+
+
+# name -> (restype, argtypes); this table is also what the symbol-export test walks.
+SIGNATURES: Dict[str, Tuple[object, list]] = {
+    "sb_abi_version": (i32, []),
+    "sb_last_error_string": (C.c_char_p, []),
+    "sb_device_sm_count": (i32, []),
+    "sb_last_launch_count": (i32, []),
+    "sb_router_topk": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
+    "sb_softmax_topk": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp]),
+    "sb_permute_workspace_bytes": (sz, [i32, i32]),
+    "sb_tile_table_ints": (sz, [i32, i32]),
+    "sb_permute": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, vp, vp, vp, vp]),
+    "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
+    "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
+    "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
+    "sb_moe_layer_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
+    "sb_moe_layer_forward": (i32, [C.POINTER(MoeLayer), vp, vp]),
+}
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m sparse_b200.build` "
+            "(needs nvcc); sparse_b200 has no non-CUDA fallback")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)       # AttributeError if a symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int, what: str) -> None:
+    if status != SB_OK:
+        msg = lib.sb_last_error_string()
+        raise RuntimeError(f"{what} failed with status {status}: {msg.decode() if msg else ''}")

@@ -1,0 +1,191 @@
+// extern "C" surface of libsparse_b200: argument checks, error text, the
+// whole-layer driver and the cache-slot copy.  Declarations and the reference
+// spans they replace are in include/sparse_b200.h.
+#include <stdarg.h>
+#include <string.h>
+
+#include "sb_common.cuh"
+
+namespace sb {
+
+static thread_local char g_err[512] = "";
+static thread_local int g_launches = 0;
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int32_t fail(int32_t code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void count_launch(int n) { g_launches += n; }
+void reset_launch_count() { g_launches = 0; }
+
+static inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Carves the caller's workspace; the same walk gives the required size.
+struct LayerScratch {
+  char *permute_ws; size_t permute_ws_bytes;
+  int32_t *tile_table, *expert_offsets, *slot_of_item, *item_of_slot;
+  void *slot_scale, *shared_scale, *xs, *hbuf, *y, *shared_h, *shared_out;
+  size_t total;
+  int r_cap, t_cap;
+};
+
+static LayerScratch carve(char *base, int T, int H, int E, int K, int I, int I_shared) {
+  LayerScratch s;
+  const size_t al = 1024;
+  const int n_items = T * K;
+  s.r_cap = (int)up((size_t)(n_items > 0 ? n_items : 1), SB_TILE_M);
+  s.t_cap = (int)up((size_t)(T > 0 ? T : 1), SB_TILE_M);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char *p = base + off; off += up(bytes, al); return p; };
+  s.permute_ws_bytes = sb_permute_workspace_bytes(n_items, E);
+  s.permute_ws = take(s.permute_ws_bytes);
+  s.tile_table = (int32_t *)take(sb_tile_table_ints(n_items, E) * 4);
+  s.expert_offsets = (int32_t *)take((size_t)(E + 1) * 4);
+  s.slot_of_item = (int32_t *)take((size_t)s.r_cap * 4);
+  s.item_of_slot = (int32_t *)take((size_t)s.r_cap * 4);
+  s.slot_scale = take((size_t)s.r_cap * 2);
+  s.shared_scale = take((size_t)s.t_cap * 2);
+  s.xs = take((size_t)s.r_cap * H * 2);
+  s.hbuf = take((size_t)s.r_cap * I * 2);
+  s.y = take((size_t)s.r_cap * H * 2);
+  s.shared_h = I_shared > 0 ? take((size_t)s.t_cap * I_shared * 2) : nullptr;
+  s.shared_out = I_shared > 0 ? take((size_t)s.t_cap * H * 2) : nullptr;
+  s.total = off;
+  return s;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int32_t sb_abi_version(void) { return 1; }
+
+const char *sb_last_error_string(void) { return g_err; }
+
+int32_t sb_last_launch_count(void) { return g_launches; }
+
+int32_t sb_device_sm_count(void) {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int32_t sb_router_topk(const void *x, const void *wg, const float *bias, const void *w_shared_gate,
+                       int32_t T, int32_t H, int32_t E, int32_t K, int32_t renorm, int32_t dtype,
+                       int32_t fp32_logits, int32_t *out_idx, void *out_w, void *out_logits,
+                       void *out_shared_scale, void *stream) {
+  return launch_router(x, wg, bias, w_shared_gate, T, H, E, K, renorm, dtype, fp32_logits, out_idx,
+                       out_w, out_logits, out_shared_scale, static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_softmax_topk(const void *logits, int32_t T, int32_t E, int32_t K, int32_t renorm,
+                        int32_t dtype, int32_t *out_idx, void *out_w, void *stream) {
+  return launch_softmax_topk(logits, T, E, K, renorm, dtype, out_idx, out_w,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_permute(const void *x, const int32_t *item_expert, const void *item_scale,
+                   int32_t n_items, int32_t items_per_row, int32_t H, int32_t E, void *ws,
+                   size_t ws_bytes, void *out_rows, int32_t *expert_offsets, int32_t *slot_of_item,
+                   int32_t *item_of_slot, void *slot_scale, int32_t *tile_table, void *stream) {
+  return launch_permute(x, item_expert, item_scale, n_items, items_per_row, H, E, ws, ws_bytes,
+                        out_rows, expert_offsets, slot_of_item, item_of_slot, slot_scale, tile_table,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table, int32_t dense_rows,
+                          const void *w13, const void *w2, const int32_t *slot_of_expert,
+                          const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
+                          void *hbuf, void *out, int32_t *status, void *stream) {
+  return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
+                               R_cap, H, I, S, hbuf, out, status, static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
+                   const void *shared_out, int32_t T, int32_t H, int32_t K, void *out, void *stream) {
+  return launch_combine(rows_out, slot_of_item, idx, shared_out, T, H, K, out,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_slot_copy_async(void *dst_slot, const void *src, size_t bytes, int32_t kind,
+                           int32_t device, void *stream) {
+  if (!dst_slot || !src) return fail(SB_E_INVALID_ARG, "sb_slot_copy_async: null pointer");
+  if (bytes == 0) return SB_OK;
+  cudaMemcpyKind k;
+  switch (kind) {
+    case SB_COPY_HOST_TO_DEVICE: k = cudaMemcpyHostToDevice; break;
+    case SB_COPY_PEER_TO_DEVICE: k = cudaMemcpyDefault; break;     // unified addressing finds the peer
+    case SB_COPY_DEVICE_LOCAL: k = cudaMemcpyDeviceToDevice; break;
+    default: return fail(SB_E_INVALID_ARG, "sb_slot_copy_async: unknown kind %d", kind);
+  }
+  if (device >= 0) SB_CUDA_CHECK(cudaSetDevice(device));
+  SB_CUDA_CHECK(cudaMemcpyAsync(dst_slot, src, bytes, k, static_cast<cudaStream_t>(stream)));
+  return SB_OK;
+}
+
+size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K, int32_t I,
+                                    int32_t I_shared) {
+  if (T < 0 || H <= 0 || E <= 0 || K <= 0 || I <= 0 || I_shared < 0) return 0;
+  return carve(nullptr, T, H, E, K, I, I_shared).total;
+}
+
+int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *stream_) {
+  reset_launch_count();
+  if (!L) return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: null layer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int T = L->T, H = L->H, E = L->E, K = L->K, I = L->I, Is = L->I_shared;
+  if (T < 0 || H <= 0 || E <= 0 || K <= 0 || I <= 0 || Is < 0)
+    return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: bad shape T=%d H=%d E=%d K=%d I=%d Is=%d", T, H,
+                E, K, I, Is);
+  if (T == 0) return SB_OK;
+  if (!L->x || !L->router_w || !L->w13 || !L->w2 || !L->out || !L->topk_idx || !L->topk_w || !L->ws)
+    return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: null pointer");
+  if ((Is > 0) != (L->shared_w13 != nullptr && L->shared_w2 != nullptr))
+    return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: shared weights and I_shared go together");
+  if (L->shared_gate_w && Is == 0)
+    return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: shared gate without shared expert");
+  if (!aligned(L->ws, 1024)) return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: ws must be 1024-byte aligned");
+  LayerScratch s = carve(static_cast<char *>(L->ws), T, H, E, K, I, Is);
+  if (L->ws_bytes < s.total)
+    return fail(SB_E_WORKSPACE, "sb_moe_layer_forward: workspace %zu < %zu bytes", L->ws_bytes, s.total);
+
+  int32_t rc;
+  rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
+                     SB_DTYPE_BF16, L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits,
+                     L->shared_gate_w ? s.shared_scale : nullptr, stream);
+  if (rc != SB_OK) return rc;
+  rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes,
+                      s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
+                      s.tile_table, stream);
+  if (rc != SB_OK) return rc;
+  rc = launch_grouped_swiglu(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
+                             s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
+  if (rc != SB_OK) return rc;
+  if (Is > 0) {
+    rc = launch_grouped_swiglu(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
+                               L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
+                               s.shared_out, status, stream);
+    if (rc != SB_OK) return rc;
+  }
+  return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
+                        L->out, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+// Expert-sorted token permutation: a stable counting sort of the flat
+// (token, slot) items by expert id, the gather of activation rows into that
+// order, and the row-tile table for the grouped GEMM.
+//
+// Replaces expand/argsort/gather/bincount of the reference's dispatch
+// (utils/eval_core.py:14873-14882) and the re-sort by expert in the local
+// executor (utils/eval_core.py:13240-13253).  Integer work is exact: the slot of
+// an item is (number of items of smaller expert id) + (number of earlier items
+// of the same expert), which is what a stable sort by expert id yields.
+//
+// Four launches: count (per 128-item chunk histogram) -> scan (per-expert
+// prefix over chunks, expert offsets, tile table) -> scatter (ranks inside a
+// chunk by warp match) -> gather (one warp per output row, 16-byte vectors).
+// The gather is the only HBM-heavy part: it reads T*H*2 bytes (re-reads of a
+// row hit L2) and writes n_items*H*2.
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kChunk = 128;          // items per warp-chunk
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxExperts = 256;
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+permute_count_kernel(const int32_t *__restrict__ item_expert, int n_items, int E, int nchunks,
+                     int32_t *__restrict__ counts) {
+  __shared__ int hist[kWarpsPerBlock][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * kWarpsPerBlock + warp;
+  for (int e = lane; e < E; e += 32) hist[warp][e] = 0;
+  __syncwarp();
+  if (chunk < nchunks) {
+#pragma unroll
+    for (int r = 0; r < kChunk / 32; ++r) {
+      int i = chunk * kChunk + r * 32 + lane;
+      if (i < n_items) {
+        int e = item_expert[i];
+        if (e >= 0 && e < E) atomicAdd(&hist[warp][e], 1);
+      }
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) counts[(size_t)chunk * E + e] = hist[warp][e];
+  }
+}
+
+// One CTA.  counts[c][e] becomes the number of items of expert e in chunks < c.
+__global__ void __launch_bounds__(1024)
+permute_scan_kernel(int32_t *__restrict__ counts, int nchunks, int E, int tile_cap,
+                    int32_t *__restrict__ expert_offsets, int32_t *__restrict__ tile_table) {
+  __shared__ int total[kMaxExperts];
+  __shared__ int offs[kMaxExperts + 1];
+  __shared__ int tile_start[kMaxExperts + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < E; e += 32) {
+    int running = 0;
+    for (int c0 = 0; c0 < nchunks; c0 += 32) {
+      int c = c0 + lane;
+      int v = (c < nchunks) ? counts[(size_t)c * E + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+      }
+      if (c < nchunks) counts[(size_t)c * E + e] = running + incl - v;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) total[e] = running;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, ts = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = o; tile_start[e] = ts;
+      o += total[e];
+      ts += (total[e] + SB_TILE_M - 1) / SB_TILE_M;
+    }
+    offs[E] = o; tile_start[E] = ts;
+    tile_table[0] = ts < tile_cap ? ts : tile_cap;
+    tile_table[1] = o;          // total rows
+    tile_table[2] = 0; tile_table[3] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) expert_offsets[e] = offs[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int nt = tile_start[e + 1] - tile_start[e];
+    for (int m = 0; m < nt; ++m) {
+      int ti = tile_start[e] + m;
+      if (ti >= tile_cap) break;
+      int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
+      int rb = offs[e] + m * SB_TILE_M;
+      int re = offs[e + 1] < rb + SB_TILE_M ? offs[e + 1] : rb + SB_TILE_M;
+      ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+permute_scatter_kernel(const int32_t *__restrict__ item_expert,
+                       const __nv_bfloat16 *__restrict__ item_scale, int n_items, int E,
+                       int nchunks, const int32_t *__restrict__ chunk_base,
+                       const int32_t *__restrict__ expert_offsets,
+                       int32_t *__restrict__ slot_of_item, int32_t *__restrict__ item_of_slot,
+                       __nv_bfloat16 *__restrict__ slot_scale) {
+  __shared__ int base[kWarpsPerBlock][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * kWarpsPerBlock + warp;
+  if (chunk >= nchunks) return;
+  for (int e = lane; e < E; e += 32)
+    base[warp][e] = expert_offsets[e] + chunk_base[(size_t)chunk * E + e];
+  __syncwarp();
+#pragma unroll
+  for (int r = 0; r < kChunk / 32; ++r) {
+    int i = chunk * kChunk + r * 32 + lane;
+    int e = -1;
+    if (i < n_items) { e = item_expert[i]; if (e < 0 || e >= E) e = -1; }
+    unsigned peers = __match_any_sync(0xffffffffu, e);
+    int rank = __popc(peers & ((1u << lane) - 1u));
+    int slot = -1;
+    if (e >= 0) slot = base[warp][e] + rank;
+    __syncwarp();
+    if (e >= 0 && rank == 0) base[warp][e] += __popc(peers);
+    __syncwarp();
+    if (i < n_items) {
+      slot_of_item[i] = slot;
+      if (slot >= 0) {
+        item_of_slot[slot] = i;
+        if (slot_scale != nullptr) slot_scale[slot] = item_scale[i];
+      }
+    }
+  }
+}
+
+// One warp per output row.
+__global__ void __launch_bounds__(256)
+permute_gather_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item_of_slot,
+                      const int32_t *__restrict__ expert_offsets, int E, int items_per_row,
+                      int vec_per_row, uint4 *__restrict__ out_rows) {
+  const int lane = threadIdx.x & 31;
+  const int n_rows = expert_offsets[E];
+  const int warps_total = gridDim.x * (blockDim.x >> 5);
+  for (int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < n_rows;
+       slot += warps_total) {
+    int src = item_of_slot[slot] / items_per_row;
+    const uint4 *s = x + (size_t)src * vec_per_row;
+    uint4 *d = out_rows + (size_t)slot * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+}  // namespace
+
+static inline int num_chunks(int n_items) { return (n_items + kChunk - 1) / kChunk; }
+
+int32_t launch_permute(const void *x, const int32_t *item_expert, const void *item_scale,
+                       int n_items, int items_per_row, int H, int E, void *ws, size_t ws_bytes,
+                       void *out_rows, int32_t *expert_offsets, int32_t *slot_of_item,
+                       int32_t *item_of_slot, void *slot_scale, int32_t *tile_table,
+                       cudaStream_t stream) {
+  if (n_items < 0 || items_per_row < 1 || H <= 0 || H % 8 != 0 || E < 1 || E > kMaxExperts)
+    return fail(SB_E_INVALID_ARG, "sb_permute: need H%%8==0, 1<=E<=256, items_per_row>=1 (n=%d H=%d E=%d)",
+                n_items, H, E);
+  if (!expert_offsets || !tile_table || !ws)
+    return fail(SB_E_INVALID_ARG, "sb_permute: null pointer");
+  if (n_items > 0 && (!x || !item_expert || !out_rows || !slot_of_item || !item_of_slot))
+    return fail(SB_E_INVALID_ARG, "sb_permute: null pointer");
+  if ((slot_scale != nullptr) != (item_scale != nullptr))
+    return fail(SB_E_INVALID_ARG, "sb_permute: item_scale and slot_scale go together");
+  if (ws_bytes < sb_permute_workspace_bytes(n_items, E))
+    return fail(SB_E_WORKSPACE, "sb_permute: workspace %zu < %zu bytes", ws_bytes,
+                sb_permute_workspace_bytes(n_items, E));
+  if (!aligned(x, 16) || !aligned(out_rows, 16))
+    return fail(SB_E_INVALID_ARG, "sb_permute: rows must be 16-byte aligned");
+  const int nchunks = num_chunks(n_items);
+  int32_t *counts = static_cast<int32_t *>(ws);
+  const int tile_cap = n_items / SB_TILE_M + E;
+  if (nchunks > 0) {
+    int blocks = (nchunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    permute_count_kernel<<<blocks, kWarpsPerBlock * 32, 0, stream>>>(item_expert, n_items, E,
+                                                                    nchunks, counts);
+    SB_LAUNCH_CHECK();
+  }
+  permute_scan_kernel<<<1, 1024, 0, stream>>>(counts, nchunks, E, tile_cap, expert_offsets,
+                                              tile_table);
+  SB_LAUNCH_CHECK();
+  if (nchunks > 0) {
+    int blocks = (nchunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    permute_scatter_kernel<<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
+        item_expert, static_cast<const __nv_bfloat16 *>(item_scale), n_items, E, nchunks, counts,
+        expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale));
+    SB_LAUNCH_CHECK();
+    int rows_per_block = 8;
+    int gblocks = (n_items + rows_per_block - 1) / rows_per_block;
+    int max_blocks = sb_device_sm_count() * 8;
+    if (gblocks > max_blocks) gblocks = max_blocks;
+    permute_gather_kernel<<<gblocks, 256, 0, stream>>>(
+        static_cast<const uint4 *>(x), item_of_slot, expert_offsets, E, items_per_row, H / 8,
+        static_cast<uint4 *>(out_rows));
+    SB_LAUNCH_CHECK();
+  }
+  return SB_OK;
+}
+
+}  // namespace sb
+
+extern "C" size_t sb_permute_workspace_bytes(int32_t n_items, int32_t E) {
+  size_t n = (size_t)sb::num_chunks(n_items < 0 ? 0 : n_items) * (size_t)(E < 1 ? 1 : E) * sizeof(int32_t);
+  return n < 256 ? 256 : ((n + 255) / 256) * 256;
+}
+
+extern "C" size_t sb_tile_table_ints(int32_t n_items, int32_t E) {
+  size_t tiles = (size_t)(n_items < 0 ? 0 : n_items) / SB_TILE_M + (size_t)(E < 1 ? 1 : E);
+  return sb::kTileHeaderInts + tiles * sb::kTileEntryInts;
+}

@@ -1,0 +1,340 @@
+// Router: logits (fixed fp32 summation order) -> softmax (fp32) -> top-k.
+//
+// Replaces `_routing_router` of the reference (utils/eval_core.py:9519-9520,
+// 9591-9595) plus the scalar gate of the shared expert
+// (utils/eval_core.py:9461-9462).
+//
+// Summation order of one logit (bit-exact contract with the CPU oracle): the H
+// inputs are cut into groups of 8; lane l of a warp accumulates groups
+// l, l+32, l+64, ... in increasing order, elements 0..7 of a group in order,
+// each step acc = fl(acc + fl(x*w)) (for bf16 inputs the product is exact, so a
+// fused multiply-add gives the same bits); the 32 lane sums are combined by an
+// xor-butterfly with offsets 16, 8, 4, 2, 1; the bias is added in fp32 and the
+// result is rounded once to the model dtype.
+//
+// Work split: one CTA owns TB tokens whose activations sit in shared memory;
+// each of its 8 warps streams pairs of router rows from L2 and dots them with
+// all TB tokens, so a weight row is fetched once per CTA.  HBM traffic is one
+// read of x plus the outputs; the kernel is bound by the fp32 FMA pipe
+// (2*T*E*H flops on CUDA cores), not by DRAM.
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kRouterThreads = 256;
+constexpr int kRouterWarps = kRouterThreads / 32;
+constexpr int kMaxExperts = 256;
+constexpr int kMaxK = 8;
+
+template <typename IN> struct Load8;
+
+template <> struct Load8<__nv_bfloat16> {
+  static constexpr bool kExactProduct = true;
+  __device__ static void from(const uint4 *p, float (&v)[8]) {
+    uint4 r = *p;
+    v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x); v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
+    v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z); v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
+  }
+  __device__ static void from_global(const __nv_bfloat16 *base, size_t elem, float (&v)[8]) {
+    uint4 r = __ldg(reinterpret_cast<const uint4 *>(base + elem));
+    v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x); v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
+    v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z); v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
+  }
+  __device__ static float round_model(float f) { return round_bf16(f); }
+  __device__ static void store(__nv_bfloat16 *p, float f) { *p = __float2bfloat16_rn(f); }
+  __device__ static float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+};
+
+template <> struct Load8<float> {
+  static constexpr bool kExactProduct = false;
+  __device__ static void from(const uint4 *p, float (&v)[8]) {
+    uint4 a = p[0], b = p[1];
+    v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y);
+    v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+    v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y);
+    v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+  }
+  __device__ static void from_global(const float *base, size_t elem, float (&v)[8]) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(base + elem);
+    uint4 a = __ldg(p), b = __ldg(p + 1);
+    v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y);
+    v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+    v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y);
+    v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+  }
+  __device__ static float round_model(float f) { return f; }
+  __device__ static void store(float *p, float f) { *p = f; }
+  __device__ static float load(const float *p) { return *p; }
+};
+
+__device__ __forceinline__ float butterfly_sum(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ float butterfly_max(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+// One warp: softmax over E model-dtype logits (given as fp32 values) and top-k.
+// `lg` points at this token's E logits in shared memory.
+template <typename IN>
+__device__ void warp_softmax_topk(const float *lg, int E, int K, int renorm, int lane,
+                                  int32_t *out_idx, IN *out_w) {
+  constexpr int kPerLane = kMaxExperts / 32;
+  float p[kPerLane];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    int e = lane + 32 * i;
+    p[i] = (e < E) ? lg[e] : -INFINITY;
+    m = fmaxf(m, p[i]);
+  }
+  m = butterfly_max(m);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    int e = lane + 32 * i;
+    if (e < E) { p[i] = expf(p[i] - m); s = __fadd_rn(s, p[i]); } else { p[i] = -1.f; }
+  }
+  s = butterfly_sum(s);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i)
+    if (p[i] >= 0.f) p[i] = __fdiv_rn(p[i], s);
+
+  float sel_v[kMaxK];
+  int sel_i[kMaxK];
+#pragma unroll
+  for (int k = 0; k < kMaxK; ++k) {
+    if (k >= K) break;
+    // lane-local best: larger probability, then smaller expert id
+    float bv = -2.f; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      int e = lane + 32 * i;
+      if (p[i] > bv) { bv = p[i]; bi = e; }   // ascending e: first max wins
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    sel_v[k] = bv; sel_i[k] = bi;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (lane + 32 * i == bi) p[i] = -1.f;
+  }
+  if (lane == 0) {
+    float denom = 1.f;
+    if (renorm) {
+      float t = 0.f;
+      for (int k = 0; k < K; ++k) t = __fadd_rn(t, sel_v[k]);
+      denom = fmaxf(t, 1e-12f);
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxK; ++k) {
+      if (k >= K) break;
+      float v = renorm ? __fdiv_rn(sel_v[k], denom) : sel_v[k];
+      out_idx[k] = sel_i[k];
+      Load8<IN>::store(out_w + k, v);
+    }
+  }
+}
+
+template <typename IN, int TB>
+__global__ void __launch_bounds__(kRouterThreads)
+router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *__restrict__ bias,
+              const IN *__restrict__ wsg, int T, int H, int E, int K, int renorm, int fp32_logits,
+              int32_t *__restrict__ out_idx, IN *__restrict__ out_w, void *__restrict__ out_logits,
+              IN *__restrict__ out_shared) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int kVecPerGroup = sizeof(IN) == 2 ? 1 : 2;      // uint4 per 8 elements
+  const int G = H / 8;
+  uint4 *sx = reinterpret_cast<uint4 *>(smem_raw);            // [TB][G*kVecPerGroup]
+  float *slog = reinterpret_cast<float *>(sx + (size_t)TB * G * kVecPerGroup);  // [TB][E+1]
+  const int NR = E + (wsg != nullptr ? 1 : 0);
+  const int ldl = E + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * TB;
+
+  // stage the activation tile
+  const int vec_per_tok = G * kVecPerGroup;
+  for (int i = threadIdx.x; i < TB * vec_per_tok; i += kRouterThreads) {
+    int t = i / vec_per_tok, v = i - t * vec_per_tok;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (t0 + t < T)
+      val = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(t0 + t) * H) + v);
+    sx[i] = val;
+  }
+  __syncthreads();
+
+  const int steps = (G + 31) / 32;
+  const int pairs = (NR + 1) / 2;
+  for (int pr = warp; pr < pairs; pr += kRouterWarps) {
+    const int r0 = 2 * pr, r1 = 2 * pr + 1;
+    const IN *w0 = (r0 < E) ? wg + (size_t)r0 * H : wsg;
+    const IN *w1 = (r1 < E) ? wg + (size_t)r1 * H : ((r1 < NR) ? wsg : nullptr);
+    float acc[TB][2];
+#pragma unroll
+    for (int t = 0; t < TB; ++t) { acc[t][0] = 0.f; acc[t][1] = 0.f; }
+    for (int j = 0; j < steps; ++j) {
+      const int g = j * 32 + lane;
+      if (g < G) {
+        float a[8], b[8];
+        Load8<IN>::from_global(w0, (size_t)g * 8, a);
+        if (w1 != nullptr) Load8<IN>::from_global(w1, (size_t)g * 8, b);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) b[i] = 0.f;
+        }
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+          float xv[8];
+          Load8<IN>::from(sx + ((size_t)t * G + g) * kVecPerGroup, xv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (Load8<IN>::kExactProduct) {
+              acc[t][0] = __fmaf_rn(xv[i], a[i], acc[t][0]);
+              acc[t][1] = __fmaf_rn(xv[i], b[i], acc[t][1]);
+            } else {
+              acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(xv[i], a[i]));
+              acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(xv[i], b[i]));
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+      float s0 = butterfly_sum(acc[t][0]);
+      float s1 = butterfly_sum(acc[t][1]);
+      if (lane == 0) {
+        if (r0 < E && bias != nullptr) s0 = __fadd_rn(s0, bias[r0]);
+        if (r1 < E && bias != nullptr) s1 = __fadd_rn(s1, bias[r1]);
+        // the shared gate's logit (row E) is always a model-dtype linear output
+        slog[t * ldl + r0] = (fp32_logits && r0 < E) ? s0 : Load8<IN>::round_model(s0);
+        if (r1 < NR) slog[t * ldl + r1] = (fp32_logits && r1 < E) ? s1 : Load8<IN>::round_model(s1);
+      }
+    }
+  }
+  __syncthreads();
+
+  for (int t = warp; t < TB; t += kRouterWarps) {
+    const int tok = t0 + t;
+    if (tok >= T) continue;
+    const float *lg = slog + t * ldl;
+    if (out_logits != nullptr) {
+      if (fp32_logits)
+        for (int e = lane; e < E; e += 32) static_cast<float *>(out_logits)[(size_t)tok * E + e] = lg[e];
+      else
+        for (int e = lane; e < E; e += 32)
+          Load8<IN>::store(static_cast<IN *>(out_logits) + (size_t)tok * E + e, lg[e]);
+    }
+    if (wsg != nullptr && lane == 0) {
+      float v = lg[E];
+      float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
+      Load8<IN>::store(out_shared + tok, sg);
+    }
+    warp_softmax_topk<IN>(lg, E, K, renorm, lane, out_idx + (size_t)tok * K,
+                          out_w + (size_t)tok * K);
+  }
+}
+
+template <typename IN>
+__global__ void __launch_bounds__(kRouterThreads)
+softmax_topk_kernel(const IN *__restrict__ logits, int T, int E, int K, int renorm,
+                    int32_t *__restrict__ out_idx, IN *__restrict__ out_w) {
+  __shared__ float slog[kRouterWarps][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * kRouterWarps + warp;
+  if (tok >= T) return;
+  for (int e = lane; e < E; e += 32) slog[warp][e] = Load8<IN>::load(logits + (size_t)tok * E + e);
+  __syncwarp();
+  warp_softmax_topk<IN>(slog[warp], E, K, renorm, lane, out_idx + (size_t)tok * K,
+                        out_w + (size_t)tok * K);
+}
+
+template <typename IN, int TB>
+int32_t launch_router_tb(const void *x, const void *wg, const float *bias, const void *wsg, int T,
+                         int H, int E, int K, int renorm, int fp32_logits, int32_t *out_idx,
+                         void *out_w, void *out_logits, void *out_shared, cudaStream_t stream) {
+  size_t smem = (size_t)TB * H * sizeof(IN) + (size_t)TB * (E + 1) * sizeof(float);
+  auto kern = router_kernel<IN, TB>;
+  if (smem > 48 * 1024)
+    SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int blocks = (T + TB - 1) / TB;
+  kern<<<blocks, kRouterThreads, smem, stream>>>(
+      static_cast<const IN *>(x), static_cast<const IN *>(wg), bias, static_cast<const IN *>(wsg),
+      T, H, E, K, renorm, fp32_logits, out_idx, static_cast<IN *>(out_w), out_logits,
+      static_cast<IN *>(out_shared));
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+template <typename IN>
+int32_t launch_router_t(const void *x, const void *wg, const float *bias, const void *wsg, int T,
+                        int H, int E, int K, int renorm, int fp32_logits, int32_t *out_idx,
+                        void *out_w, void *out_logits, void *out_shared, cudaStream_t stream) {
+  // Fewer tokens per CTA when there are few tokens, so decode-sized calls still
+  // spread over the SMs; 16 per CTA at prefill sizes to amortise the weight reads.
+  const size_t tile16 = (size_t)16 * H * sizeof(IN) + 16 * (size_t)(E + 1) * 4;
+  if (T >= 2048 && tile16 <= 200 * 1024)
+    return launch_router_tb<IN, 16>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
+                                    out_w, out_logits, out_shared, stream);
+  if (T >= 256)
+    return launch_router_tb<IN, 4>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
+                                   out_w, out_logits, out_shared, stream);
+  return launch_router_tb<IN, 1>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx, out_w,
+                                 out_logits, out_shared, stream);
+}
+
+}  // namespace
+
+int32_t launch_router(const void *x, const void *wg, const float *bias, const void *wsg, int T,
+                      int H, int E, int K, int renorm, int dtype, int fp32_logits, int32_t *out_idx,
+                      void *out_w, void *out_logits, void *out_shared_scale, cudaStream_t stream) {
+  if (T < 0 || H <= 0 || H % 8 != 0 || E < 1 || E > kMaxExperts || K < 1 || K > kMaxK || K > E)
+    return fail(SB_E_INVALID_ARG, "sb_router_topk: need H%%8==0, 1<=K<=8, K<=E<=256 (T=%d H=%d E=%d K=%d)",
+                T, H, E, K);
+  if (T == 0) return SB_OK;
+  if (!x || !wg || !out_idx || !out_w) return fail(SB_E_INVALID_ARG, "sb_router_topk: null pointer");
+  if ((wsg != nullptr) != (out_shared_scale != nullptr))
+    return fail(SB_E_INVALID_ARG, "sb_router_topk: w_shared_gate and out_shared_scale go together");
+  if (!aligned(x, 16) || !aligned(wg, 16) || (wsg && !aligned(wsg, 16)))
+    return fail(SB_E_INVALID_ARG, "sb_router_topk: x, wg, w_shared_gate must be 16-byte aligned");
+  if ((size_t)H * (dtype == SB_DTYPE_F32 ? 4 : 2) + (E + 1) * 4 > 200 * 1024)
+    return fail(SB_E_UNSUPPORTED, "sb_router_topk: hidden size %d too large for the token tile", H);
+  if (dtype == SB_DTYPE_BF16)
+    return launch_router_t<__nv_bfloat16>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
+                                          out_w, out_logits, out_shared_scale, stream);
+  if (dtype == SB_DTYPE_F32)
+    return launch_router_t<float>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx, out_w,
+                                  out_logits, out_shared_scale, stream);
+  return fail(SB_E_INVALID_ARG, "sb_router_topk: unknown dtype %d", dtype);
+}
+
+int32_t launch_softmax_topk(const void *logits, int T, int E, int K, int renorm, int dtype,
+                            int32_t *out_idx, void *out_w, cudaStream_t stream) {
+  if (T < 0 || E < 1 || E > kMaxExperts || K < 1 || K > kMaxK || K > E)
+    return fail(SB_E_INVALID_ARG, "sb_softmax_topk: need 1<=K<=8, K<=E<=256 (T=%d E=%d K=%d)", T, E, K);
+  if (T == 0) return SB_OK;
+  if (!logits || !out_idx || !out_w) return fail(SB_E_INVALID_ARG, "sb_softmax_topk: null pointer");
+  int blocks = (T + kRouterWarps - 1) / kRouterWarps;
+  if (dtype == SB_DTYPE_BF16)
+    softmax_topk_kernel<__nv_bfloat16><<<blocks, kRouterThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(logits), T, E, K, renorm, out_idx,
+        static_cast<__nv_bfloat16 *>(out_w));
+  else if (dtype == SB_DTYPE_F32)
+    softmax_topk_kernel<float><<<blocks, kRouterThreads, 0, stream>>>(
+        static_cast<const float *>(logits), T, E, K, renorm, out_idx, static_cast<float *>(out_w));
+  else
+    return fail(SB_E_INVALID_ARG, "sb_softmax_topk: unknown dtype %d", dtype);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+}  // namespace sb
