@@ -203,6 +203,10 @@ typedef struct sb_moe_layer {
   void *ws; size_t ws_bytes;     /* sb_moe_layer_workspace_bytes() */
 } sb_moe_layer;
 
+/* sizeof(sb_moe_layer) as this library was compiled, so a binding can check
+ * its mirror of the struct. */
+size_t sb_moe_layer_struct_bytes(void);
+
 size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K,
                                     int32_t I, int32_t I_shared);
 

@@ -51,6 +51,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
+    "sb_moe_layer_struct_bytes": (sz, []),
     "sb_moe_layer_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "sb_moe_layer_forward": (i32, [C.POINTER(MoeLayer), vp, vp]),
 }
@@ -70,6 +71,8 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
+if lib.sb_moe_layer_struct_bytes() != C.sizeof(MoeLayer):
+    raise ImportError("sparse_b200: struct sb_moe_layer of the library and its ctypes mirror differ")
 
 
 def check(status: int, what: str) -> None:

@@ -140,6 +140,8 @@ int32_t sb_slot_copy_async(void *dst_slot, const void *src, size_t bytes, int32_
   return SB_OK;
 }
 
+size_t sb_moe_layer_struct_bytes(void) { return sizeof(sb_moe_layer); }
+
 size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K, int32_t I,
                                     int32_t I_shared) {
   if (T < 0 || H <= 0 || E <= 0 || K <= 0 || I <= 0 || I_shared < 0) return 0;
