@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""MoE-layer throughput on B200: tokens/s through one Qwen1.5-MoE-shaped block.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the MoE layer hot path (router top-k -> expert-sorted
+permute -> grouped SwiGLU GEMMs for routed and shared experts -> combine) over
+one batch of synthetic tokens.  Workload at every N: per GPU 4096 tokens of
+hidden states ~N(0,1) in bf16, weights N(0,0.02) seed 0, router bias
+log Zipf(1.2) over a seeded expert permutation (weak scaling; at N>1 the 60
+experts are sharded round-robin over the N GPUs and rows travel by all-to-all).
+
+Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in
+HBM; `e2e` goes through the block-level API with pinned HOST buffers, the
+host->device and device->host copies inside the timed region.  `roofline`
+describes the dominant kernel (the grouped tcgen05 GEMM, tensor-bound at this
+size); `stages` breaks a step into its kernels with achieved HBM GB/s for the
+memory-bound ones.  `--impl reference` times the CPU restatement of the
+reference block on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+TOKENS_PER_GPU = 4096
+ZIPF_S = 1.2
+WORKLOAD = "qwen1.5-moe-a2.7b-shaped MoE block, bf16, %d tokens/GPU, zipf(1.2) router bias" % TOKENS_PER_GPU
+CPU_SAMPLE_TOKENS = 512
+N_INPUT_BATCHES = 4          # rotated so a step never re-reads the previous step's activations
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
+# kernel (the gate/up pass of the routed grouped GEMM: 678.2 MB read + 44.7 MB
+# written), from the ncu capture summarised in profiles/grouped_gemm_qwen_t4096.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 722976256
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def start(self):
+        if self._nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def _physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ------------------------------------------------------------------ CPU arm ----
+
+def cpu_reference_tokens_per_s(steps: int, warmup: int):
+    """The reference block's CPU path (fp32, world=1) restated by the oracle,
+    on all host cores, over a bounded sample of the workload."""
+    from oracle import moe_oracle as mo
+    from sparse_b200 import synth
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shape = synth.QWEN_MOE
+    w = synth.make_weights(shape, weight_seed=0, zipf_s=ZIPF_S)
+    cw = mo.cast_weights(w, torch.float32)
+    x = synth.make_hidden(TOKENS_PER_GPU, shape.hidden, seed=1)[:CPU_SAMPLE_TOKENS].contiguous()
+    with torch.no_grad():
+        for _ in range(max(1, warmup)):
+            mo.moe_block_forward(x, cw, shape.top_k, router="library")
+        t0 = time.perf_counter()
+        for _ in range(max(1, steps)):
+            mo.moe_block_forward(x, cw, shape.top_k, router="library")
+        dt = time.perf_counter() - t0
+    per_step = dt / max(1, steps)
+    return CPU_SAMPLE_TOKENS / per_step, per_step * 1e3, torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(max(1, args.steps), 20)
+    warmup = min(max(1, args.warmup), 3)
+    tps, ms, cores = cpu_reference_tokens_per_s(steps, warmup)
+    sample = "first %d of the %d tokens, fp32, %d steps" % (CPU_SAMPLE_TOKENS, TOKENS_PER_GPU, steps)
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ GPU arm ----
+
+def _time_region(fn, steps, stream):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(steps):
+        fn(i)
+    end.record(stream)
+    end.synchronize()
+    return start.elapsed_time(end)      # ms
+
+
+def stage_breakdown(lw, shape, xs, steps):
+    """Per-kernel device time of one step through the per-stage entry points."""
+    from sparse_b200 import ops
+    dev = lw.device
+    stream = torch.cuda.current_stream(dev)
+    t, k, e, h, i, ish = xs[0].shape[0], shape.top_k, shape.num_experts, shape.hidden, shape.inter, shape.shared_inter
+    x = xs[0]
+    idx, wts, _, sg = ops.router_topk(x, lw.router_w, k, bias=lw.router_bias, w_shared_gate=lw.shared_gate_w)
+    p = ops.permute(x, idx.reshape(-1), e, k, item_scale=wts.reshape(-1))
+    y, _ = ops.grouped_swiglu(p.rows, lw.w13, lw.w2, tile_table=p.tile_table,
+                              slot_of_expert=lw.slot_of_expert, row_scale=p.slot_scale)
+    ys, _ = ops.grouped_swiglu(x, lw.shared_w13, lw.shared_w2, dense_rows=t, row_scale=sg)
+    torch.cuda.synchronize()
+    out = {}
+    reps = max(5, min(steps, 50))
+
+    def timed(name, fn):
+        for _ in range(3):
+            fn(0)
+        out[name] = _time_region(fn, reps, stream) / reps
+
+    timed("router_topk", lambda j: ops.router_topk(xs[j % len(xs)], lw.router_w, k, bias=lw.router_bias,
+                                                   w_shared_gate=lw.shared_gate_w))
+    timed("permute", lambda j: ops.permute(xs[j % len(xs)], idx.reshape(-1), e, k, item_scale=wts.reshape(-1)))
+    timed("routed_swiglu", lambda j: ops.grouped_swiglu(p.rows, lw.w13, lw.w2, tile_table=p.tile_table,
+                                                        slot_of_expert=lw.slot_of_expert, row_scale=p.slot_scale))
+    timed("shared_swiglu", lambda j: ops.grouped_swiglu(xs[j % len(xs)], lw.shared_w13, lw.shared_w2,
+                                                        dense_rows=t, row_scale=sg))
+    timed("combine", lambda j: ops.combine(y, p.slot_of_item, idx, ys, t))
+    n = t * k
+    distinct = int((p.expert_offsets[1:] != p.expert_offsets[:-1]).sum().item())
+    bytes_ = {
+        "router_topk": t * h * 2 + (e + 1) * h * 2 + t * k * 6 + t * e * 2 + t * 2,
+        "permute": t * h * 2 + n * h * 2 + n * 14,
+        "combine": n * h * 2 + n * 8 + t * h * 2 + t * h * 2,
+    }
+    flops = {
+        "routed_swiglu": 2 * n * h * 2 * i + 2 * n * i * h,
+        "shared_swiglu": 2 * t * h * 2 * ish + 2 * t * ish * h,
+    }
+    return out, bytes_, flops, distinct
+
+
+def run_ours(args):
+    from sparse_b200 import synth
+    from sparse_b200.block import B200MoeBlock
+    from sparse_b200.layer import LayerRunner, LayerWeights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if args.gpus != 1 and world == 1:
+            raise SystemExit("bench.py --gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist = dist_
+        dist.init_process_group(backend="nccl", device_id=dev)
+
+    peaks = _peaks()
+    shape = synth.QWEN_MOE
+    t = TOKENS_PER_GPU
+    w = synth.make_weights(shape, weight_seed=0, zipf_s=ZIPF_S)
+    block = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=t,
+                                            process_group=None if world == 1 else dist.group.WORLD)
+    xs_host = [synth.make_hidden(t, shape.hidden, seed=1 + 97 * rank + b).to(torch.bfloat16).pin_memory()
+               for b in range(N_INPUT_BATCHES)]
+    xs = [xh.to(dev) for xh in xs_host]
+    out_host = torch.empty((t, shape.hidden), dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        v = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    # ---- device-resident throughput ----
+    def step_dev(i):
+        block.forward_device(xs[i % N_INPUT_BATCHES])
+
+    for i in range(max(3, args.warmup)):
+        step_dev(i)
+    barrier()
+    sampler = ClockSampler(_physical_gpu_index(local_rank))
+    sampler.start()
+    ms_dev = _time_region(step_dev, args.steps, stream)
+    barrier()
+    ms_dev = max_over_ranks(ms_dev)
+    launches = block.last_launches * args.steps
+    block.check_status()
+
+    # ---- end to end through the host-buffer API ----
+    def step_e2e(i):
+        block.forward_host(xs_host[i % N_INPUT_BATCHES], out_host)
+
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    t0 = time.perf_counter()
+    ms_e2e_dev = _time_region(step_e2e, args.steps, stream)
+    torch.cuda.synchronize()
+    ms_e2e_wall = (time.perf_counter() - t0) * 1e3
+    ms_e2e = max_over_ranks(max(ms_e2e_dev, ms_e2e_wall))
+    sampler.stop()
+    barrier()
+
+    total_tokens = t * world * args.steps
+    value = total_tokens / (ms_dev * 1e-3)
+    e2e_value = total_tokens / (ms_e2e * 1e-3)
+
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_dev / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": t, "experts": shape.num_experts,
+                   "top_k": shape.top_k, "hidden": shape.hidden, "inter": shape.inter,
+                   "shared_inter": shape.shared_inter,
+                   "parallelism": "ep%d" % world if world > 1 else "ep1",
+                   "l2": "weights 1.1 GB per layer exceed the 126 MB L2; %d input batches rotated" % N_INPUT_BATCHES},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": t * shape.hidden * 2 * world,
+                "d2h_bytes_per_step": t * shape.hidden * 2 * world},
+        "gpu_launches": launches,
+        "clocks": sampler.summary(),
+    }
+
+    if rank == 0:
+        # per-kernel breakdown and roofline of the dominant kernel (single-GPU kernels)
+        lw = block.weights
+        stage_ms, stage_bytes, stage_flops, distinct = stage_breakdown(lw, shape, xs, args.steps)
+        stages = {}
+        for name, ms in stage_ms.items():
+            ent = {"ms": ms}
+            if name in stage_bytes:
+                gbs = stage_bytes[name] / (ms * 1e-3) / 1e9
+                ent.update({"bytes": stage_bytes[name], "gb_s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]})
+            if name in stage_flops:
+                tf = stage_flops[name] / (ms * 1e-3) / 1e12
+                ent.update({"flops": stage_flops[name], "tflop_s": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]})
+            stages[name] = ent
+        line["stages"] = stages
+        gemm_flops = stage_flops["routed_swiglu"] + stage_flops["shared_swiglu"]
+        gemm_ms = stage_ms["routed_swiglu"] + stage_ms["shared_swiglu"]
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        line["roofline"] = {
+            "bound": "tensor", "kernel": "grouped_gemm_kernel (tcgen05, 4 launches per step)",
+            "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_tflops"], "peak_source": "%s (burst cuBLAS bf16)" % peaks["source"],
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "flops_per_step": gemm_flops, "ms_per_step": gemm_ms,
+        }
+        # whole-layer roofline: slower of dense compute at peak and HBM bytes at peak
+        layer_flops = shape.flops_per_token() * t
+        hbm_bytes = distinct * shape.routed_expert_bytes_bf16 + 3 * shape.hidden * shape.shared_inter * 2 \
+            + 2 * t * shape.hidden * 2
+        t_roof = max(layer_flops / (peaks["bf16_tflops"] * 1e12), hbm_bytes / (peaks["hbm_gbs"] * 1e9))
+        line["layer_roofline"] = {"roofline_ms": t_roof * 1e3, "measured_ms": ms_dev / args.steps,
+                                  "frac": t_roof * 1e3 / (ms_dev / args.steps),
+                                  "distinct_experts": distinct}
+        if world == 1 and not args.no_cpu_baseline:
+            tps, ms, cores = cpu_reference_tokens_per_s(3, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": "first %d of the %d tokens, fp32, 3 steps after 1 warm-up" % (
+                                        CPU_SAMPLE_TOKENS, t)}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,112 @@
+"""Block-level API of the B200 MoE layer.
+
+`B200MoeBlock` is the object a serving loop holds per MoE layer: it owns the
+layer's device weights, the scratch of the layer pass and (for expert
+parallelism) the peer-memory buffers, and exposes
+
+    forward_device(x_dev)          -> out_dev            inputs already in HBM
+    forward_host(x_pinned, out_pinned)                    host buffers, copies included
+    forward(hidden_states[B,S,H])  -> (out, router_logits) | out
+                                      the `DistributedSparseMoeBlock.forward`
+                                      contract (utils/eval_core.py:16418-16563)
+
+Everything it computes goes through the C ABI; there is no eager fallback.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .layer import LayerRunner, LayerWeights
+
+
+class B200MoeBlock:
+    def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int,
+                 norm_topk_prob: bool = False, fp32_router_logits: bool = False,
+                 return_router_logits: bool = True, ep_rank: int = 0, ep_size: int = 1,
+                 process_group=None):
+        self.weights = weights
+        self.device = weights.device
+        self.top_k = top_k
+        self.ep_rank, self.ep_size = ep_rank, ep_size
+        self.return_router_logits = return_router_logits
+        self.runner = LayerRunner(weights, top_k, max_tokens, renorm=norm_topk_prob,
+                                  fp32_logits=fp32_router_logits, want_logits=True)
+        self._ep = None
+        if ep_size > 1:
+            from .ep import ExpertParallelLayer
+            self._ep = ExpertParallelLayer(weights, top_k, max_tokens, ep_rank, ep_size,
+                                           process_group, renorm=norm_topk_prob,
+                                           fp32_logits=fp32_router_logits)
+        self._x_stage: Optional[torch.Tensor] = None
+        self.last_launches = 0
+
+    @classmethod
+    def from_block_weights(cls, w, device: torch.device, ep_rank: int = 0, ep_size: int = 1,
+                           max_tokens: int = 4096, process_group=None) -> "B200MoeBlock":
+        """Build from seeded `synth.BlockWeights`; at ep_size > 1 only the
+        experts owned by `ep_rank` (round-robin, e % ep_size) are loaded."""
+        s = w.shape
+        if ep_size == 1:
+            lw = LayerWeights.from_block_weights(w, device)
+        else:
+            owned = [e for e in range(s.num_experts) if e % ep_size == ep_rank]
+            lw = LayerWeights(s.hidden, s.inter, s.num_experts, len(owned), s.shared_inter, device)
+            lw.set_router(w.router, w.router_bias)
+            slot_of = [-1] * s.num_experts
+            for slot, e in enumerate(owned):
+                lw.load_expert(slot, w.gate[e], w.up[e], w.down[e])
+                slot_of[e] = slot
+            lw.set_slot_map(slot_of)
+            if s.shared_inter:
+                lw.set_shared(w.sh_gate, w.sh_up, w.sh_down, w.sh_scalar_gate)
+        return cls(lw, s.top_k, max_tokens, norm_topk_prob=s.norm_topk_prob,
+                   fp32_router_logits=not s.shared_gate and s.num_experts == 64,
+                   ep_rank=ep_rank, ep_size=ep_size, process_group=process_group)
+
+    # -- the three entry points -----------------------------------------------------
+    def forward_device(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._ep is not None:
+            res = self._ep.forward(x, out)
+            self.last_launches = self._ep.last_launches
+            return res
+        res, _, _, _ = self.runner.forward(x, out)
+        self.last_launches = self.runner.last_launches
+        return res
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """x_host, out_host: pinned bf16 [T,H].  Copies in, runs the layer, copies
+        the result out; returns when `out_host` is valid."""
+        t, h = x_host.shape
+        if self._x_stage is None or self._x_stage.shape[0] < t:
+            self._x_stage = torch.empty((max(t, self.runner.max_tokens), h), dtype=torch.bfloat16,
+                                        device=self.device)
+        xd = self._x_stage[:t]
+        xd.copy_(x_host, non_blocking=True)
+        out = self.forward_device(xd)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def forward(self, hidden_states: torch.Tensor):
+        b, s, h = hidden_states.shape
+        x = hidden_states.reshape(-1, h)
+        if x.dtype != torch.bfloat16:
+            raise RuntimeError("B200MoeBlock computes in bf16; got %s" % x.dtype)
+        out = torch.empty_like(x)
+        self.forward_device(x.contiguous(), out)
+        out = out.view(b, s, h)
+        if not self.return_router_logits:
+            return out
+        return out, self.router_logits(x.shape[0])
+
+    def router_logits(self, tokens: int) -> torch.Tensor:
+        src = self._ep.logits if self._ep is not None else self.runner.logits
+        return src[:tokens]
+
+    def topk(self, tokens: int):
+        r = self._ep if self._ep is not None else self.runner
+        return r.topk_idx[:tokens], r.topk_w[:tokens]
+
+    def check_status(self) -> None:
+        (self._ep or self.runner).check_status()
