@@ -128,6 +128,36 @@ int32_t sb_permute(const void *x, const int32_t *item_expert, const void *item_s
                    int32_t *tile_table, void *stream);
 
 /*
+ * sb_permute for callers that cannot hand over scratch memory.  (No counterpart
+ * in the reference: it has no allocation-free mode.)
+ *
+ * Some hosts of this library must not allocate device memory on the serving
+ * path: a decode loop in which cudaMalloc would stall every stream of the
+ * device, or a process whose memory pool (PyTorch's caching allocator, a
+ * framework arena) already owns all of HBM so that a raw allocation fails or
+ * fragments it.  sb_permute asks such a caller for a workspace it may have no
+ * way to get.  This variant takes none: the per-chunk histograms live in a
+ * 512 KiB array inside the library's device image, which every GPU that loads
+ * the library holds until the process exits.  Inputs and outputs are still the
+ * caller's; the call itself runs no cudaMalloc, cudaFree or other allocating
+ * routine.  Results are identical to sb_permute.
+ *
+ * Limit: ceil(n_items/128) * E <= 131072 (e.g. 262144 items over 64 experts);
+ * larger problems are refused with SB_E_WORKSPACE and a message.
+ * The first call on each device looks up the array's device address (with that
+ * device current); make that first call before starting any stream capture.
+ * All calls on a device share the one array and nothing in it needs clearing
+ * between calls, but two calls that overlap on the GPU (different streams)
+ * race on it: keep calls on one stream or order them with events.
+ */
+int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
+                           const void *item_scale, int32_t n_items,
+                           int32_t items_per_row, int32_t H, int32_t E,
+                           void *out_rows, int32_t *expert_offsets,
+                           int32_t *slot_of_item, int32_t *item_of_slot,
+                           void *slot_scale, int32_t *tile_table, void *stream);
+
+/*
  * Grouped SwiGLU expert MLP on the tensor cores (tcgen05, TMEM accumulators,
  * TMA-fed): for every row tile of `tile_table`
  *     h   = bf16( bf16(silu(bf16(x.Wg^T))) * bf16(x.Wu^T) )

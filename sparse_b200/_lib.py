@@ -48,6 +48,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_permute_workspace_bytes": (sz, [i32, i32]),
     "sb_tile_table_ints": (sz, [i32, i32]),
     "sb_permute": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, vp, vp, vp, vp]),
+    "sb_permute_noalloc": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),

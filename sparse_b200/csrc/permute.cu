@@ -204,6 +204,56 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
 
 }  // namespace sb
 
+// ---- sb_permute_noalloc: the same sort with library-owned scratch -----------------
+//
+// Scratch for the per-chunk histograms of sb_permute, reserved in the library's
+// own device image instead of being passed in.  512 KiB; every GPU that loads
+// the library carries it until the process exits.
+constexpr int kStaticScratchInts = 131072;
+static __device__ __align__(256) int32_t g_permute_scratch[kStaticScratchInts];
+
+// Device address of g_permute_scratch per device ordinal (0 = not looked up yet).
+// In host code the symbol's name is only a handle; the address a kernel can use
+// has to be asked for, with that device current.
+static int32_t *g_permute_scratch_addr[64];
+
+extern "C" int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
+                                      const void *item_scale, int32_t n_items,
+                                      int32_t items_per_row, int32_t H, int32_t E, void *out_rows,
+                                      int32_t *expert_offsets, int32_t *slot_of_item,
+                                      int32_t *item_of_slot, void *slot_scale,
+                                      int32_t *tile_table, void *stream) {
+  if (n_items < 0 || E < 1 || E > sb::kMaxExperts)
+    return sb::fail(SB_E_INVALID_ARG, "sb_permute_noalloc: need n_items>=0 and 1<=E<=256 (n=%d E=%d)",
+                    n_items, E);
+  const size_t need_ints = (size_t)sb::num_chunks(n_items) * (size_t)E;
+  if (need_ints > (size_t)kStaticScratchInts)
+    return sb::fail(SB_E_WORKSPACE,
+                    "sb_permute_noalloc: %d items over %d experts need %zu scratch ints, the built-in "
+                    "scratch holds %d (ceil(n_items/128)*E must not exceed it); use sb_permute with a "
+                    "caller-provided workspace",
+                    n_items, E, need_ints, kStaticScratchInts);
+  int dev = -1;
+  SB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return sb::fail(SB_E_UNSUPPORTED, "sb_permute_noalloc: device ordinal %d", dev);
+  if (g_permute_scratch_addr[dev] == nullptr) {
+    int32_t *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_permute_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return sb::fail(SB_E_CUDA, "sb_permute_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                      cudaGetErrorString(e));
+    g_permute_scratch_addr[dev] = p;
+  }
+  // Nothing in the scratch has to start at zero: the count pass overwrites every
+  // histogram cell the later passes read, so stale contents of an earlier call
+  // are never observed.
+  return sb::launch_permute(x, item_expert, item_scale, n_items, items_per_row, H, E,
+                            g_permute_scratch_addr[dev],
+                            (size_t)kStaticScratchInts * sizeof(int32_t), out_rows, expert_offsets,
+                            slot_of_item, item_of_slot, slot_scale, tile_table,
+                            static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t sb_permute_workspace_bytes(int32_t n_items, int32_t E) {
   size_t n = (size_t)sb::num_chunks(n_items < 0 ? 0 : n_items) * (size_t)(E < 1 ? 1 : E) * sizeof(int32_t);
   return n < 256 ? 256 : ((n + 255) / 256) * 256;
