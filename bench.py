@@ -315,11 +315,37 @@ def run_ours(args):
         "clocks": sampler.summary(),
     }
 
+    # ---- per-stage breakdown (all ranks run it; rank 0 reports) ----
+    ep_marks = None
+    if world > 1:
+        ep_layer = block._ep
+        reps = max(3, min(args.steps, 20))
+        ep_layer.stage_events = []
+        for i in range(reps):
+            step_dev(i)
+        barrier()
+        ep_marks = ep_layer.stage_events
+        ep_layer.stage_events = None
+        recv_rows = int(ep_layer.r.recv_offsets[-1].item())
+
     if rank == 0:
-        # per-kernel breakdown and roofline of the dominant kernel (single-GPU kernels)
-        lw = block.weights
-        stage_ms, stage_bytes, stage_flops, distinct = stage_breakdown(lw, shape, xs, args.steps)
         stages = {}
+        if world == 1:
+            lw = block.weights
+            stage_ms, stage_bytes, stage_flops, distinct = stage_breakdown(lw, shape, xs, args.steps)
+        else:
+            per = len(ep_marks) // reps
+            stage_ms = {}
+            for rep in range(reps):
+                chunk = ep_marks[rep * per:(rep + 1) * per]
+                for (n0, e0), (n1, e1) in zip(chunk[:-1], chunk[1:]):
+                    stage_ms[n1] = stage_ms.get(n1, 0.0) + e0.elapsed_time(e1) / reps
+            n_recv = recv_rows
+            h, i, ish = shape.hidden, shape.inter, shape.shared_inter
+            stage_bytes = {}
+            stage_flops = {"routed_swiglu": 2 * n_recv * h * 2 * i + 2 * n_recv * i * h,
+                           "shared_swiglu": 2 * t * h * 2 * ish + 2 * t * ish * h}
+            distinct = len([e for e in range(shape.num_experts) if e % world == rank])
         for name, ms in stage_ms.items():
             ent = {"ms": ms}
             if name in stage_bytes:
@@ -337,17 +363,22 @@ def run_ours(args):
             "bound": "tensor", "kernel": "grouped_gemm_kernel (tcgen05, 4 launches per step)",
             "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_tflops"], "peak_source": "%s (burst cuBLAS bf16)" % peaks["source"],
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
             "flops_per_step": gemm_flops, "ms_per_step": gemm_ms,
         }
-        # whole-layer roofline: slower of dense compute at peak and HBM bytes at peak
+        # whole-layer roofline per GPU: slower of dense compute at peak and
+        # (HBM bytes at HBM peak + NVLink bytes at 900 GB/s per direction)
         layer_flops = shape.flops_per_token() * t
         hbm_bytes = distinct * shape.routed_expert_bytes_bf16 + 3 * shape.hidden * shape.shared_inter * 2 \
             + 2 * t * shape.hidden * 2
-        t_roof = max(layer_flops / (peaks["bf16_tflops"] * 1e12), hbm_bytes / (peaks["hbm_gbs"] * 1e9))
+        nvlink_bytes = 0 if world == 1 else t * shape.top_k * (world - 1) / world * shape.hidden * 2
+        t_mem = hbm_bytes / (peaks["hbm_gbs"] * 1e9) + 2 * nvlink_bytes / 900e9
+        t_roof = max(layer_flops / (peaks["bf16_tflops"] * 1e12), t_mem)
         line["layer_roofline"] = {"roofline_ms": t_roof * 1e3, "measured_ms": ms_dev / args.steps,
                                   "frac": t_roof * 1e3 / (ms_dev / args.steps),
-                                  "distinct_experts": distinct}
+                                  "distinct_experts": distinct,
+                                  "nvlink_bytes_per_gpu_per_direction": nvlink_bytes,
+                                  "nvlink_peak": "900 GB/s per direction (datasheet)"}
         if world == 1 and not args.no_cpu_baseline:
             tps, ms, cores = cpu_reference_tokens_per_s(3, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",

@@ -112,7 +112,8 @@ size_t sb_tile_table_ints(int32_t n_items, int32_t E);
  *   item_expert    [n_items] int32 in [0,E); a negative id drops the item
  *   item_scale     [n_items] bf16 route weight per item, or NULL
  *   ws             scratch of sb_permute_workspace_bytes()
- *   out_rows       [n_items,H] bf16, rows in expert-sorted order
+ *   out_rows       [n_items,H] bf16, rows in expert-sorted order; NULL = sort
+ *                  only, no rows are gathered (x may then be NULL too)
  *   expert_offsets [E+1] int32
  *   slot_of_item   [n_items] int32 (-1 for dropped items)
  *   item_of_slot   [n_items] int32
@@ -210,6 +211,68 @@ int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item,
  */
 int32_t sb_slot_copy_async(void *dst_slot, const void *src, size_t bytes,
                            int32_t kind, int32_t device, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Expert parallelism over NVLink peer memory (one process per GPU).
+ * Together these replace `_experts_ep_group`'s dispatch and return halves:
+ * expand/argsort/bincount, the count all-to-all with its two host syncs, the
+ * three payload all-to-alls, the local re-sort, the return all-to-all and the
+ * unsort (utils/eval_core.py:14865-14900, 14999-15019, 13240-13253,
+ * 15048-15060), and `_resolve_dest_for_flat_experts` (6736-6769) through the
+ * `owner` table.
+ *
+ * Set-up calls (these DO allocate / synchronise; call them once, outside the
+ * serving loop):
+ *   sb_peer_alloc   zero-filled device buffer that can be exported
+ *   sb_ipc_export   64-byte handle of such a buffer, to send to the other ranks
+ *   sb_ipc_import   peer's buffer mapped into this process (peer access enabled)
+ * Every rank then holds, per shared buffer, an array of `ep` device pointers
+ * indexed by rank (its own entry is the local pointer); these arrays are HOST
+ * arrays, passed by value into the kernels.
+ * ------------------------------------------------------------------------ */
+int32_t sb_peer_alloc(size_t bytes, void **out_ptr);
+int32_t sb_peer_free(void *ptr);
+int32_t sb_ipc_export(const void *ptr, void *handle64);
+int32_t sb_ipc_import(const void *handle64, void **out_ptr);
+int32_t sb_ipc_close(void *ptr);
+
+/* Write this rank's per-expert item counts (differences of `local_offsets`
+ * [E+1], as produced by sb_permute) into row `rank` of every rank's counts
+ * matrix int32 [ep][E]. */
+int32_t sb_ep_publish_counts(const int32_t *local_offsets, int32_t E, int32_t rank,
+                             int32_t ep, void *const *peer_counts, void *stream);
+
+/* Stream-ordered barrier across the ranks: flags are uint32 [ep] per rank in
+ * peer memory, `epoch` increases by one per call on every rank.  The wait is
+ * bounded (2 s); on expiry `status` (device int32, may be NULL) becomes 3. */
+int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t epoch,
+                      int32_t *status, void *stream);
+
+/* From the complete counts matrix: where this rank's items of each expert start
+ * in the owner's receive buffer (`dst_base` [E]), and this rank's own
+ * receive-side segments (`recv_offsets` [E+1], tile table as in sb_permute,
+ * sized by sb_tile_table_ints(recv_cap, E)).  Receive buffers are laid out by
+ * expert id, then source rank, then the source's stable item order. */
+int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, int32_t rank,
+                   int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
+                   int32_t *tile_table, void *stream);
+
+/* Copy every item's activation row and route weight into its row of the
+ * owner's receive buffers (`peer_rows[d]` [recv_cap,H] bf16, `peer_scale[d]`
+ * [recv_cap] bf16) and remember where it went (`item_rank`, `item_row` [n_items]).
+ * `slot_of_item` / `local_offsets` come from sb_permute on the local items. */
+int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *item_scale,
+                       const int32_t *slot_of_item, const int32_t *local_offsets,
+                       const int32_t *dst_base, const int32_t *owner, int32_t n_items,
+                       int32_t items_per_row, int32_t H, int32_t ep, int32_t recv_cap,
+                       void *const *peer_rows, void *const *peer_scale, int32_t *item_rank,
+                       int32_t *item_row, void *stream);
+
+/* sb_combine with the K rows of a token read from the owners' output buffers
+ * (`peer_y[d]` [recv_cap,H] bf16). */
+int32_t sb_ep_combine(void *const *peer_y, const int32_t *item_rank, const int32_t *item_row,
+                      const int32_t *idx, const void *shared_out, int32_t T, int32_t H,
+                      int32_t K, int32_t ep, void *out, void *stream);
 
 /* Everything one single-GPU layer pass needs; all pointers are device
  * pointers owned by the caller. */

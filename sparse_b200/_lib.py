@@ -52,6 +52,17 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
+    "sb_peer_alloc": (i32, [sz, C.POINTER(vp)]),
+    "sb_peer_free": (i32, [vp]),
+    "sb_ipc_export": (i32, [vp, vp]),
+    "sb_ipc_import": (i32, [vp, C.POINTER(vp)]),
+    "sb_ipc_close": (i32, [vp]),
+    "sb_ep_publish_counts": (i32, [vp, i32, i32, i32, C.POINTER(vp), vp]),
+    "sb_ep_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, vp, vp]),
+    "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
+    "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                             C.POINTER(vp), C.POINTER(vp), vp, vp, vp]),
+    "sb_ep_combine": (i32, [C.POINTER(vp), vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sb_moe_layer_struct_bytes": (sz, []),
     "sb_moe_layer_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "sb_moe_layer_forward": (i32, [C.POINTER(MoeLayer), vp, vp]),

@@ -1,0 +1,362 @@
+// Expert-parallel dispatch and combine over NVLink peer memory.
+//
+// Replaces the reference's five `all_to_all_single` calls per layer, the two
+// host syncs between them and the local re-sort of received rows
+// (utils/eval_core.py:14865-15060, 13240-13253).  One process per GPU; every
+// rank maps the receive buffers of all ranks (CUDA IPC) and moves rows with
+// plain peer stores and loads inside its own kernels:
+//
+//   publish   each rank writes its per-expert item counts into every rank's
+//             counts matrix [ep][E]                                  (peer stores)
+//   barrier   flag exchange in peer memory, bounded wait
+//   plan      from the counts matrix every rank derives, without talking again,
+//             where each (source rank, expert) segment lives in the owner's
+//             receive buffer: the buffer is laid out expert-major, then source
+//             rank, then the source's stable item order, so rows ARRIVE
+//             expert-sorted and the owner needs no second sort; also the
+//             owner's row-tile table for the grouped GEMM
+//   dispatch  one warp per item copies the token's activation row and route
+//             weight straight into its final row of the owner's buffer
+//   barrier   rows have landed
+//   (grouped GEMM on the owner, on its own rows)
+//   barrier   outputs are complete
+//   combine   each token reads its K output rows from the owners' buffers and
+//             adds them in ascending expert id (bf16-sequential), plus the
+//             shared expert's row
+//
+// No host synchronisation and no size negotiation: the receive buffers are
+// sized for the worst case (every item of every rank to one owner).
+// Wire bytes per remote (token, expert) pair: H*2 out, H*2 back, 2 for the
+// route weight.
+//
+// The barrier's spin is bounded (2 s); on expiry it writes `status` = 3 and
+// returns.  Ranks are separate processes on separate GPUs; two ranks of this
+// barrier must never share one GPU.
+#include <string.h>
+
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kMaxRanks = 16;
+constexpr int kMaxExperts = 256;
+constexpr int kMaxK = 8;
+constexpr unsigned long long kBarrierLimitNs = 2000000000ull;
+
+struct PeerPtrs { void *p[kMaxRanks]; };
+
+__device__ __forceinline__ unsigned long long gtimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// counts_all on every rank: [ep][E]; this rank fills row `rank` everywhere.
+__global__ void ep_publish_kernel(const int32_t *__restrict__ local_offsets, int E, int rank, int ep,
+                                  PeerPtrs counts_all) {
+  for (int i = threadIdx.x; i < E * ep; i += blockDim.x) {
+    int p = i / E, e = i - p * E;
+    int32_t *dst = static_cast<int32_t *>(counts_all.p[p]) + (size_t)rank * E + e;
+    *dst = local_offsets[e + 1] - local_offsets[e];
+  }
+}
+
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epoch,
+                                  int32_t *__restrict__ status) {
+  const int p = threadIdx.x;
+  if (p >= ep) return;
+  __threadfence_system();
+  uint32_t *remote = static_cast<uint32_t *>(flags.p[p]) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const uint32_t *mine = static_cast<const uint32_t *>(flags.p[rank]) + p;
+  const unsigned long long t0 = gtimer_ns();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - epoch) >= 0) break;
+    if (gtimer_ns() - t0 > kBarrierLimitNs) {
+      if (status) atomicExch(status, 3);
+      break;
+    }
+    __nanosleep(100);
+  }
+  __threadfence_system();
+}
+
+// One CTA.  Reads the complete counts matrix of this rank and writes
+//   dst_base[e]  first row, in owner(e)'s receive buffer, of THIS rank's items of expert e
+//   recv_offsets[E+1], tile table: this rank's receive-side expert segments
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict__ owner, int E,
+               int rank, int ep, int tile_cap, int32_t *__restrict__ dst_base,
+               int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table) {
+  __shared__ int tot[kMaxExperts];        // items of expert e over all sources
+  __shared__ int before_me[kMaxExperts];  // items of expert e from sources < rank
+  __shared__ int seg_begin[kMaxExperts];  // first row of expert e in its owner's buffer
+  __shared__ int my_off[kMaxExperts + 1]; // receive-side offsets on this rank (0 for foreign experts)
+  __shared__ int tile_start[kMaxExperts + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (int s = 0; s < ep; ++s) {
+      int c = counts_all[(size_t)s * E + e];
+      if (s < rank) b += c;
+      t += c;
+    }
+    tot[e] = t; before_me[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < ep) {
+    // per owner: running offset over its experts in ascending id
+    const int d = threadIdx.x;
+    int run = 0;
+    for (int e = 0; e < E; ++e)
+      if (owner[e] == d) { seg_begin[e] = run; run += tot[e]; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ts = 0, last = 0;
+    for (int e = 0; e < E; ++e) {
+      const bool mine = owner[e] == rank;
+      my_off[e] = mine ? seg_begin[e] : last;
+      tile_start[e] = ts;
+      if (mine) { last = seg_begin[e] + tot[e]; ts += (tot[e] + SB_TILE_M - 1) / SB_TILE_M; }
+    }
+    my_off[E] = last; tile_start[E] = ts;
+    tile_table[0] = ts < tile_cap ? ts : tile_cap;
+    tile_table[1] = last;
+    tile_table[2] = 0; tile_table[3] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) dst_base[e] = seg_begin[e] + before_me[e];
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) recv_offsets[e] = my_off[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    if (owner[e] != rank) continue;
+    const int nt = tile_start[e + 1] - tile_start[e];
+    for (int m = 0; m < nt; ++m) {
+      const int ti = tile_start[e] + m;
+      if (ti >= tile_cap) break;
+      int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
+      const int rb = seg_begin[e] + m * SB_TILE_M;
+      const int re = min(seg_begin[e] + tot[e], rb + SB_TILE_M);
+      ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
+    }
+  }
+}
+
+// One warp per item: activation row and route weight to the owner's buffer.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item_expert,
+                   const __nv_bfloat16 *__restrict__ item_scale,
+                   const int32_t *__restrict__ slot_of_item, const int32_t *__restrict__ local_offsets,
+                   const int32_t *__restrict__ dst_base, const int32_t *__restrict__ owner,
+                   int n_items, int items_per_row, int vec_per_row, int recv_cap, PeerPtrs recv_rows,
+                   PeerPtrs recv_scale, int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * (blockDim.x >> 5);
+  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_items; i += warps_total) {
+    const int e = item_expert[i];
+    const int slot = slot_of_item[i];
+    if (e < 0 || slot < 0) {
+      if (lane == 0) { item_rank[i] = -1; item_row[i] = -1; }
+      continue;
+    }
+    const int d = owner[e];
+    const int row = dst_base[e] + (slot - local_offsets[e]);
+    if (row >= recv_cap) {             // cannot happen with worst-case sizing; never write past the buffer
+      if (lane == 0) { item_rank[i] = -1; item_row[i] = -1; }
+      continue;
+    }
+    const uint4 *s = x + (size_t)(i / items_per_row) * vec_per_row;
+    uint4 *dp = static_cast<uint4 *>(recv_rows.p[d]) + (size_t)row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) dp[v] = __ldg(s + v);
+    if (lane == 0) {
+      static_cast<__nv_bfloat16 *>(recv_scale.p[d])[row] = item_scale[i];
+      item_rank[i] = d; item_row[i] = row;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+  return pack_bf16x2(__fadd_rn(bf16_lo(a), bf16_lo(b)), __fadd_rn(bf16_hi(a), bf16_hi(b)));
+}
+__device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
+  return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w));
+}
+
+// One CTA per token; rows come from the owners' output buffers.
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(PeerPtrs y_rows, const int32_t *__restrict__ item_rank,
+                  const int32_t *__restrict__ item_row, const int32_t *__restrict__ idx,
+                  const uint4 *__restrict__ shared_out, int T, int vec_per_row, int K,
+                  uint4 *__restrict__ out) {
+  __shared__ const uint4 *s_src[kMaxK];
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    if (threadIdx.x == 0) {
+      int eid[kMaxK]; const uint4 *src[kMaxK];
+      for (int k = 0; k < K; ++k) {
+        const int i = t * K + k;
+        const int e = idx[i], d = item_rank[i], r = item_row[i];
+        const uint4 *p = (d >= 0) ? static_cast<const uint4 *>(y_rows.p[d]) + (size_t)r * vec_per_row : nullptr;
+        int j = k;
+        while (j > 0 && eid[j - 1] > e) { eid[j] = eid[j - 1]; src[j] = src[j - 1]; --j; }
+        eid[j] = e; src[j] = p;
+      }
+      for (int k = 0; k < K; ++k) s_src[k] = src[k];
+    }
+    __syncthreads();
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      uint4 acc = make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < K; ++k) {
+        const uint4 *p = s_src[k];
+        if (p != nullptr) acc = add8(acc, p[v]);
+      }
+      if (shared_out != nullptr) acc = add8(acc, __ldg(shared_out + (size_t)t * vec_per_row + v));
+      out[(size_t)t * vec_per_row + v] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+int32_t fill_peers(PeerPtrs *pp, void *const *ptrs, int ep, const char *what) {
+  if (ep < 1 || ep > kMaxRanks) return fail(SB_E_INVALID_ARG, "%s: ep=%d outside [1,%d]", what, ep, kMaxRanks);
+  for (int i = 0; i < kMaxRanks; ++i) pp->p[i] = nullptr;
+  for (int i = 0; i < ep; ++i) {
+    if (!ptrs || !ptrs[i]) return fail(SB_E_INVALID_ARG, "%s: null peer pointer %d", what, i);
+    pp->p[i] = ptrs[i];
+  }
+  return SB_OK;
+}
+
+}  // namespace
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int32_t sb_peer_alloc(size_t bytes, void **out_ptr) {
+  if (!out_ptr || bytes == 0) return fail(SB_E_INVALID_ARG, "sb_peer_alloc: bad arguments");
+  void *p = nullptr;
+  SB_CUDA_CHECK(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) { cudaFree(p); return fail(SB_E_CUDA, "sb_peer_alloc: memset: %s", cudaGetErrorString(e)); }
+  SB_CUDA_CHECK(cudaDeviceSynchronize());
+  *out_ptr = p;
+  return SB_OK;
+}
+
+int32_t sb_peer_free(void *ptr) {
+  if (ptr) SB_CUDA_CHECK(cudaFree(ptr));
+  return SB_OK;
+}
+
+int32_t sb_ipc_export(const void *ptr, void *handle64) {
+  if (!ptr || !handle64) return fail(SB_E_INVALID_ARG, "sb_ipc_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  SB_CUDA_CHECK(cudaIpcGetMemHandle(&h, const_cast<void *>(ptr)));
+  memcpy(handle64, &h, 64);
+  return SB_OK;
+}
+
+int32_t sb_ipc_import(const void *handle64, void **out_ptr) {
+  if (!handle64 || !out_ptr) return fail(SB_E_INVALID_ARG, "sb_ipc_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void *p = nullptr;
+  SB_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out_ptr = p;
+  return SB_OK;
+}
+
+int32_t sb_ipc_close(void *ptr) {
+  if (ptr) SB_CUDA_CHECK(cudaIpcCloseMemHandle(ptr));
+  return SB_OK;
+}
+
+int32_t sb_ep_publish_counts(const int32_t *local_offsets, int32_t E, int32_t rank, int32_t ep,
+                             void *const *peer_counts, void *stream) {
+  if (!local_offsets || E < 1 || E > kMaxExperts || rank < 0 || rank >= ep)
+    return fail(SB_E_INVALID_ARG, "sb_ep_publish_counts: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
+  PeerPtrs pc;
+  int32_t rc = fill_peers(&pc, peer_counts, ep, "sb_ep_publish_counts");
+  if (rc != SB_OK) return rc;
+  ep_publish_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(local_offsets, E, rank, ep, pc);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t epoch,
+                      int32_t *status, void *stream) {
+  if (rank < 0 || rank >= ep) return fail(SB_E_INVALID_ARG, "sb_ep_barrier: rank=%d ep=%d", rank, ep);
+  PeerPtrs pf;
+  int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier");
+  if (rc != SB_OK) return rc;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, epoch, status);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, int32_t rank,
+                   int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
+                   int32_t *tile_table, void *stream) {
+  if (!counts_all || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 || E > kMaxExperts ||
+      rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_plan: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
+  const int tile_cap = recv_cap / SB_TILE_M + E;
+  ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, owner, E, rank, ep, tile_cap,
+                                                                   dst_base, recv_offsets, tile_table);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *item_scale,
+                       const int32_t *slot_of_item, const int32_t *local_offsets,
+                       const int32_t *dst_base, const int32_t *owner, int32_t n_items,
+                       int32_t items_per_row, int32_t H, int32_t ep, int32_t recv_cap,
+                       void *const *peer_rows, void *const *peer_scale, int32_t *item_rank,
+                       int32_t *item_row, void *stream) {
+  if (n_items < 0 || H <= 0 || H % 8 != 0 || items_per_row < 1)
+    return fail(SB_E_INVALID_ARG, "sb_ep_dispatch: bad shape (n=%d H=%d)", n_items, H);
+  if (n_items == 0) return SB_OK;
+  if (!x || !item_expert || !item_scale || !slot_of_item || !local_offsets || !dst_base || !owner ||
+      !item_rank || !item_row)
+    return fail(SB_E_INVALID_ARG, "sb_ep_dispatch: null pointer");
+  PeerPtrs pr, ps;
+  int32_t rc;
+  if ((rc = fill_peers(&pr, peer_rows, ep, "sb_ep_dispatch")) != SB_OK) return rc;
+  if ((rc = fill_peers(&ps, peer_scale, ep, "sb_ep_dispatch")) != SB_OK) return rc;
+  int blocks = (n_items + 7) / 8;
+  const int max_blocks = sb_device_sm_count() * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  ep_dispatch_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),
+      slot_of_item, local_offsets, dst_base, owner, n_items, items_per_row, H / 8, recv_cap, pr, ps,
+      item_rank, item_row);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_combine(void *const *peer_y, const int32_t *item_rank, const int32_t *item_row,
+                      const int32_t *idx, const void *shared_out, int32_t T, int32_t H, int32_t K,
+                      int32_t ep, void *out, void *stream) {
+  if (T < 0 || H <= 0 || H % 8 != 0 || K < 1 || K > kMaxK)
+    return fail(SB_E_INVALID_ARG, "sb_ep_combine: bad shape (T=%d H=%d K=%d)", T, H, K);
+  if (T == 0) return SB_OK;
+  if (!item_rank || !item_row || !idx || !out) return fail(SB_E_INVALID_ARG, "sb_ep_combine: null pointer");
+  PeerPtrs py;
+  int32_t rc = fill_peers(&py, peer_y, ep, "sb_ep_combine");
+  if (rc != SB_OK) return rc;
+  int blocks = T;
+  const int max_blocks = sb_device_sm_count() * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
+  const int threads = H / 8 >= 256 ? 256 : ((H / 8 + 31) / 32) * 32;
+  ep_combine_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      py, item_rank, item_row, idx, static_cast<const uint4 *>(shared_out), T, H / 8, K,
+      static_cast<uint4 *>(out));
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+}  // extern "C"

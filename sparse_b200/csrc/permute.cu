@@ -163,7 +163,8 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
                 n_items, H, E);
   if (!expert_offsets || !tile_table || !ws)
     return fail(SB_E_INVALID_ARG, "sb_permute: null pointer");
-  if (n_items > 0 && (!x || !item_expert || !out_rows || !slot_of_item || !item_of_slot))
+  // out_rows == NULL: sort only, no row gather (x may then be NULL as well)
+  if (n_items > 0 && (!item_expert || !slot_of_item || !item_of_slot || (out_rows && !x)))
     return fail(SB_E_INVALID_ARG, "sb_permute: null pointer");
   if ((slot_scale != nullptr) != (item_scale != nullptr))
     return fail(SB_E_INVALID_ARG, "sb_permute: item_scale and slot_scale go together");
@@ -190,14 +191,16 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
         item_expert, static_cast<const __nv_bfloat16 *>(item_scale), n_items, E, nchunks, counts,
         expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale));
     SB_LAUNCH_CHECK();
-    int rows_per_block = 8;
-    int gblocks = (n_items + rows_per_block - 1) / rows_per_block;
-    int max_blocks = sb_device_sm_count() * 8;
-    if (gblocks > max_blocks) gblocks = max_blocks;
-    permute_gather_kernel<<<gblocks, 256, 0, stream>>>(
-        static_cast<const uint4 *>(x), item_of_slot, expert_offsets, E, items_per_row, H / 8,
-        static_cast<uint4 *>(out_rows));
-    SB_LAUNCH_CHECK();
+    if (out_rows != nullptr) {
+      int rows_per_block = 8;
+      int gblocks = (n_items + rows_per_block - 1) / rows_per_block;
+      int max_blocks = sb_device_sm_count() * 8;
+      if (gblocks > max_blocks) gblocks = max_blocks;
+      permute_gather_kernel<<<gblocks, 256, 0, stream>>>(
+          static_cast<const uint4 *>(x), item_of_slot, expert_offsets, E, items_per_row, H / 8,
+          static_cast<uint4 *>(out_rows));
+      SB_LAUNCH_CHECK();
+    }
   }
   return SB_OK;
 }

@@ -1,0 +1,358 @@
+"""Expert-parallel layer pass: tokens sharded by rank, experts sharded by owner,
+rows moved by this library's own kernels over NVLink peer memory.
+
+One process per GPU.  Each rank allocates four exportable buffers (receive
+rows, receive route weights, expert outputs, counts + flags), exchanges their
+CUDA IPC handles once through `torch.distributed` (the only use of the process
+group on this path), and from then on a layer pass is a fixed sequence of
+kernel launches on one stream with no host synchronisation:
+
+    router -> local sort -> publish counts -> barrier -> plan -> dispatch
+           -> shared expert (overlaps the peers' dispatch) -> barrier
+           -> grouped SwiGLU on the received rows -> barrier -> combine
+
+The receive buffers are reused by every layer; the barriers order the reuse
+(a rank cannot start writing into a peer's buffer for the next pass before
+that peer has passed the previous pass's last barrier).
+
+`EpRank.stage_*` are the individual steps; `ExpertParallelLayer.forward` strings
+them together with barriers.  The stages can also be driven for several
+simulated ranks inside one process (all "peer" buffers on one GPU, no barrier
+kernels, the caller steps the ranks in lockstep), which is how the index
+arithmetic is tested on a single GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+from .layer import LayerWeights
+
+_TILE = _lib.SB_TILE_M
+
+
+def _round_up(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+def recv_capacity(max_tokens: int, top_k: int, ep: int) -> int:
+    """Rows a rank must be able to receive: every item of every rank."""
+    return _round_up(max(1, max_tokens * top_k * ep), _TILE)
+
+
+def plan_layout_reference(counts_all: torch.Tensor, owner: torch.Tensor, rank: int):
+    """Host mirror of `sb_ep_plan` (integer arithmetic on CPU tensors), used by the
+    debug checks and the CPU tests.  counts_all int [ep,E], owner int [E].
+    Returns (dst_base [E], recv_offsets [E+1], seg_begin [E]): rows of expert e
+    coming from source s sit at seg_begin[e] + sum(counts_all[:s, e]) in the
+    owner's receive buffer; the buffer is ordered by expert id, then source rank,
+    then the source's stable item order."""
+    counts_all = counts_all.to(torch.long)
+    owner = owner.to(torch.long)
+    ep, e = counts_all.shape
+    tot = counts_all.sum(0)
+    seg_begin = torch.zeros(e, dtype=torch.long)
+    for d in range(ep):
+        mine = (owner == d).nonzero().flatten()
+        run = torch.cumsum(tot[mine], 0) - tot[mine]
+        seg_begin[mine] = run
+    before = counts_all[:rank].sum(0)
+    dst_base = seg_begin + before
+    recv_offsets = torch.zeros(e + 1, dtype=torch.long)
+    last = 0
+    for ex in range(e):
+        if int(owner[ex]) == rank:
+            recv_offsets[ex] = seg_begin[ex]
+            last = int(seg_begin[ex] + tot[ex])
+        else:
+            recv_offsets[ex] = last
+    recv_offsets[e] = last
+    return dst_base, recv_offsets, seg_begin
+
+
+class PeerBuffers:
+    """This rank's exportable buffers and the pointers of every rank's copies."""
+
+    NAMES = ("rows", "scale", "y", "ctl")
+
+    def __init__(self, hidden: int, num_experts: int, recv_cap: int, ep: int, rank: int):
+        self.hidden, self.num_experts, self.recv_cap, self.ep, self.rank = hidden, num_experts, recv_cap, ep, rank
+        self.sizes = {
+            "rows": recv_cap * hidden * 2,
+            "scale": _round_up(recv_cap * 2, 256),
+            "y": recv_cap * hidden * 2,
+            # counts matrix int32 [ep][E] followed (at a 256-byte boundary) by the barrier flags uint32 [ep]
+            "ctl": _round_up(ep * num_experts * 4, 256) + 256,
+        }
+        self.flags_offset = _round_up(ep * num_experts * 4, 256)
+        self.local = {}
+        self.peers = {n: [0] * ep for n in self.NAMES}
+        self._owned: List[int] = []
+        self._imported: List[int] = []
+
+    def allocate_local(self) -> None:
+        for n in self.NAMES:
+            p = C.c_void_p()
+            check(lib.sb_peer_alloc(self.sizes[n], C.byref(p)), "sb_peer_alloc")
+            self.local[n] = int(p.value)
+            self._owned.append(int(p.value))
+            self.peers[n][self.rank] = int(p.value)
+
+    def export_handles(self) -> bytes:
+        out = b""
+        for n in self.NAMES:
+            buf = C.create_string_buffer(64)
+            check(lib.sb_ipc_export(self.local[n], buf), "sb_ipc_export")
+            out += buf.raw
+        return out
+
+    def import_handles(self, peer: int, blob: bytes) -> None:
+        for i, n in enumerate(self.NAMES):
+            p = C.c_void_p()
+            h = C.create_string_buffer(blob[64 * i:64 * (i + 1)], 64)
+            check(lib.sb_ipc_import(h, C.byref(p)), "sb_ipc_import")
+            self.peers[n][peer] = int(p.value)
+            self._imported.append(int(p.value))
+
+    def adopt_local_peer(self, peer: int, other: "PeerBuffers") -> None:
+        """Simulated ranks inside one process: the peer's buffers are ordinary local pointers."""
+        for n in self.NAMES:
+            self.peers[n][peer] = other.local[n]
+
+    def ptr_array(self, name: str, offset: int = 0):
+        arr = (C.c_void_p * self.ep)()
+        for i, p in enumerate(self.peers[name]):
+            arr[i] = p + offset
+        return arr
+
+    def close(self) -> None:
+        for p in self._imported:
+            lib.sb_ipc_close(p)
+        for p in self._owned:
+            lib.sb_peer_free(p)
+        self._imported, self._owned = [], []
+
+
+def exchange_handles(bufs: PeerBuffers, group) -> None:
+    """All ranks swap IPC handles through the process group (set-up time only)."""
+    import torch.distributed as dist
+    blobs: List[Optional[bytes]] = [None] * bufs.ep
+    dist.all_gather_object(blobs, bufs.export_handles(), group=group)
+    for peer, blob in enumerate(blobs):
+        if peer != bufs.rank:
+            bufs.import_handles(peer, blob)
+
+
+class EpRank:
+    """State and stages of one rank's layer pass."""
+
+    def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int, rank: int, ep: int,
+                 owner: Sequence[int], bufs: PeerBuffers, renorm: bool = False,
+                 fp32_logits: bool = False):
+        self.w, self.top_k, self.rank, self.ep = weights, top_k, rank, ep
+        self.renorm, self.fp32_logits = renorm, fp32_logits
+        self.bufs = bufs
+        dev = weights.device
+        self.device = dev
+        e, h = weights.num_experts, weights.hidden
+        self.max_tokens = max_tokens
+        n = max_tokens * top_k
+        i32, bf = torch.int32, torch.bfloat16
+        self.owner = torch.tensor(list(owner), dtype=i32, device=dev)
+        self.topk_idx = torch.empty((max_tokens, top_k), dtype=i32, device=dev)
+        self.topk_w = torch.empty((max_tokens, top_k), dtype=bf, device=dev)
+        self.logits = torch.empty((max_tokens, e), dtype=torch.float32 if fp32_logits else bf, device=dev)
+        self.shared_scale = torch.empty((_round_up(max_tokens, _TILE),), dtype=bf, device=dev)
+        self.local_offsets = torch.empty((e + 1,), dtype=i32, device=dev)
+        self.slot_of_item = torch.empty((max(n, 1),), dtype=i32, device=dev)
+        self.item_of_slot = torch.empty((max(n, 1),), dtype=i32, device=dev)
+        self.local_tiles = torch.empty((lib.sb_tile_table_ints(n, e),), dtype=i32, device=dev)
+        self.sort_ws = torch.empty((lib.sb_permute_workspace_bytes(n, e),), dtype=torch.uint8, device=dev)
+        self.dst_base = torch.empty((e,), dtype=i32, device=dev)
+        self.recv_offsets = torch.empty((e + 1,), dtype=i32, device=dev)
+        self.recv_tiles = torch.empty((lib.sb_tile_table_ints(bufs.recv_cap, e),), dtype=i32, device=dev)
+        self.item_rank = torch.empty((max(n, 1),), dtype=i32, device=dev)
+        self.item_row = torch.empty((max(n, 1),), dtype=i32, device=dev)
+        self.hbuf = torch.empty((bufs.recv_cap, weights.inter), dtype=bf, device=dev)
+        t_cap = _round_up(max_tokens, _TILE)
+        self.shared_h = self.shared_out = None
+        if weights.shared_inter:
+            self.shared_h = torch.empty((t_cap, weights.shared_inter), dtype=bf, device=dev)
+            self.shared_out = torch.empty((t_cap, h), dtype=bf, device=dev)
+        self.out = torch.empty((max_tokens, h), dtype=bf, device=dev)
+        self.status = torch.zeros((1,), dtype=i32, device=dev)
+        self.launches = 0
+        self._x = None
+        self._t = 0
+
+    def _s(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    # -- stages -------------------------------------------------------------------
+    def stage_route(self, x: torch.Tensor) -> None:
+        w, t, k = self.w, x.shape[0], self.top_k
+        if t > self.max_tokens:
+            raise RuntimeError("EP layer was sized for %d tokens, got %d" % (self.max_tokens, t))
+        self._x, self._t = x, t
+        check(lib.sb_router_topk(
+            x.data_ptr(), w.router_w.data_ptr(),
+            w.router_bias.data_ptr() if w.router_bias is not None else None,
+            w.shared_gate_w.data_ptr() if w.shared_gate_w is not None else None,
+            t, w.hidden, w.num_experts, k, int(self.renorm), _lib.SB_DTYPE_BF16, int(self.fp32_logits),
+            self.topk_idx.data_ptr(), self.topk_w.data_ptr(), self.logits.data_ptr(),
+            self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, self._s()),
+            "sb_router_topk")
+        check(lib.sb_permute(
+            None, self.topk_idx.data_ptr(), None, t * k, k, w.hidden, w.num_experts,
+            self.sort_ws.data_ptr(), self.sort_ws.numel(), None, self.local_offsets.data_ptr(),
+            self.slot_of_item.data_ptr(), self.item_of_slot.data_ptr(), None,
+            self.local_tiles.data_ptr(), self._s()), "sb_permute")
+        self.launches += 4
+
+    def stage_publish(self) -> None:
+        check(lib.sb_ep_publish_counts(self.local_offsets.data_ptr(), self.w.num_experts, self.rank,
+                                       self.ep, self.bufs.ptr_array("ctl"), self._s()),
+              "sb_ep_publish_counts")
+        self.launches += 1
+
+    def stage_barrier(self, epoch: int) -> None:
+        check(lib.sb_ep_barrier(self.bufs.ptr_array("ctl", self.bufs.flags_offset), self.rank, self.ep,
+                                epoch, self.status.data_ptr(), self._s()), "sb_ep_barrier")
+        self.launches += 1
+
+    def stage_plan(self) -> None:
+        check(lib.sb_ep_plan(self.bufs.local["ctl"], self.owner.data_ptr(), self.w.num_experts,
+                             self.rank, self.ep, self.bufs.recv_cap, self.dst_base.data_ptr(),
+                             self.recv_offsets.data_ptr(), self.recv_tiles.data_ptr(), self._s()),
+              "sb_ep_plan")
+        self.launches += 1
+
+    def stage_dispatch(self) -> None:
+        w, t, k = self.w, self._t, self.top_k
+        check(lib.sb_ep_dispatch(
+            self._x.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(),
+            self.slot_of_item.data_ptr(), self.local_offsets.data_ptr(), self.dst_base.data_ptr(),
+            self.owner.data_ptr(), t * k, k, w.hidden, self.ep, self.bufs.recv_cap,
+            self.bufs.ptr_array("rows"), self.bufs.ptr_array("scale"), self.item_rank.data_ptr(),
+            self.item_row.data_ptr(), self._s()), "sb_ep_dispatch")
+        self.launches += 1
+
+    def stage_shared(self) -> None:
+        w, t = self.w, self._t
+        if not w.shared_inter or t == 0:
+            return
+        check(lib.sb_grouped_swiglu(
+            self._x.data_ptr(), None, t, w.shared_w13.data_ptr(), w.shared_w2.data_ptr(), None,
+            self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, t, w.hidden,
+            w.shared_inter, 1, self.shared_h.data_ptr(), self.shared_out.data_ptr(),
+            self.status.data_ptr(), self._s()), "sb_grouped_swiglu(shared)")
+        self.launches += 2
+
+    def stage_experts(self) -> None:
+        w, b = self.w, self.bufs
+        check(lib.sb_grouped_swiglu(
+            b.local["rows"], self.recv_tiles.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
+            w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
+            self.hbuf.data_ptr(), b.local["y"], self.status.data_ptr(), self._s()),
+            "sb_grouped_swiglu(routed)")
+        self.launches += 2
+
+    def stage_combine(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w, t, k = self.w, self._t, self.top_k
+        dst = self.out[:t] if out is None else out
+        check(lib.sb_ep_combine(
+            self.bufs.ptr_array("y"), self.item_rank.data_ptr(), self.item_row.data_ptr(),
+            self.topk_idx.data_ptr(), self.shared_out.data_ptr() if w.shared_inter else None, t,
+            w.hidden, k, self.ep, dst.data_ptr(), self._s()), "sb_ep_combine")
+        self.launches += 1
+        return dst
+
+
+class ExpertParallelLayer:
+    """One rank of a multi-process expert-parallel layer."""
+
+    _shared_bufs = {}     # (device, hidden, experts, recv_cap, ep) -> PeerBuffers, reused by all layers
+
+    def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int, rank: int, ep: int,
+                 process_group, owner: Optional[Sequence[int]] = None, renorm: bool = False,
+                 fp32_logits: bool = False):
+        if owner is None:
+            owner = [e % ep for e in range(weights.num_experts)]
+        cap = recv_capacity(max_tokens, top_k, ep)
+        key = (str(weights.device), weights.hidden, weights.num_experts, cap, ep)
+        bufs = self._shared_bufs.get(key)
+        if bufs is None:
+            with torch.cuda.device(weights.device):
+                bufs = PeerBuffers(weights.hidden, weights.num_experts, cap, ep, rank)
+                bufs.allocate_local()
+                exchange_handles(bufs, process_group)
+            bufs.epoch = 0
+            self._shared_bufs[key] = bufs
+        self.bufs = bufs
+        self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits)
+        self.last_launches = 0
+
+    @property
+    def logits(self):
+        return self.r.logits
+
+    @property
+    def topk_idx(self):
+        return self.r.topk_idx
+
+    @property
+    def topk_w(self):
+        return self.r.topk_w
+
+    def _barrier(self) -> None:
+        self.bufs.epoch += 1
+        self.r.stage_barrier(self.bufs.epoch)
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        r = self.r
+        r.launches = 0
+        marks = self.stage_events
+        stream = torch.cuda.current_stream(r.device)
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                marks.append((name, ev))
+
+        with torch.cuda.device(r.device):
+            mark("begin")
+            r.stage_route(x)
+            mark("router+sort")
+            r.stage_publish()
+            self._barrier()
+            mark("publish+barrier")
+            r.stage_plan()
+            r.stage_dispatch()
+            mark("plan+dispatch")
+            r.stage_shared()
+            mark("shared_swiglu")
+            self._barrier()
+            mark("barrier(rows landed)")
+            r.stage_experts()
+            mark("routed_swiglu")
+            self._barrier()
+            mark("barrier(outputs ready)")
+            res = r.stage_combine(out)
+            mark("combine")
+        self.last_launches = r.launches
+        return res
+
+    # When set to a list, forward() appends (stage name, CUDA event) marks to it.
+    stage_events = None
+
+    def check_status(self) -> None:
+        s = int(self.r.status.item())
+        if s != 0:
+            self.r.status.zero_()
+            raise RuntimeError("sparse_b200 EP device status %d (1: GEMM wait expired, 2: expert "
+                               "without a weight slot, 3: peer barrier wait expired)" % s)

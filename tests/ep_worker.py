@@ -1,0 +1,44 @@
+"""One rank of the multi-GPU expert-parallel parity check (launched by
+tests/test_gpu_ep.py through torch.distributed.run)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from sparse_b200 import synth  # noqa: E402
+from sparse_b200.block import B200MoeBlock  # noqa: E402
+from sparse_b200.layer import LayerRunner, LayerWeights  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    for shape_name, tokens in (("TINY", 97 + 13 * rank), ("QWEN_MOE", 512)):
+        shape = getattr(synth, shape_name)
+        w = synth.make_weights(shape, weight_seed=0, zipf_s=1.2)
+        blk = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=tokens + 64,
+                                              process_group=dist.group.WORLD)
+        ref = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, tokens)
+        for it in range(3):          # several passes reuse the peer buffers
+            x = synth.make_hidden(tokens, shape.hidden, seed=100 * it + rank).to(torch.bfloat16).to(dev)
+            out = blk.forward_device(x).clone()
+            want, want_idx, _, _ = ref.forward(x)
+            torch.cuda.synchronize()
+            blk.check_status()
+            idx, _ = blk.topk(tokens)
+            assert torch.equal(idx, want_idx), "indices differ on rank %d" % rank
+            assert torch.equal(out, want), "EP rows differ from the single-GPU layer on rank %d" % rank
+        dist.barrier()
+    print("EP_WORKER_OK rank %d" % rank, flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
