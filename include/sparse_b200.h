@@ -171,7 +171,10 @@ int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
  *                 `dense_rows` rows using weight slot 0 (shared expert)
  *   w13           [S, 2*I, H] bf16 weight slab: per slot gate rows then up rows
  *   w2            [S, H, I]   bf16 weight slab
- *   slot_of_expert[E] int32 expert id -> weight slot, or NULL for identity
+ *   slot_of_expert[E] int32 expert id -> weight slot, or NULL for identity;
+ *                 -2 = skip this expert's tiles in this launch (they are left
+ *                 for a later launch, e.g. once its weights have arrived);
+ *                 any other negative value is an error (status = 2)
  *   row_scale     [R_cap] bf16 per-row factor, or NULL for none
  *   hbuf          [R_cap, I] bf16 scratch for the intermediate
  *   out           [R_cap, H] bf16

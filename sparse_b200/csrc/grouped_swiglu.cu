@@ -54,6 +54,10 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
+// slot_of_expert value meaning "leave this expert's tiles to another launch"
+// (readiness-ordered execution runs the grouped GEMM once per readiness class).
+constexpr int kSlotSkip = -2;
+
 constexpr int kModeSwiglu = 0;
 constexpr int kModeScale = 1;
 
@@ -239,6 +243,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const int m_tile = tile / n_ntiles, n_tile = tile - m_tile * n_ntiles;
         TileInfo ti = read_tile(tile_table, dense_rows, slot_of_expert, m_tile);
+        if (ti.slot == kSlotSkip) continue;           // not part of this launch
         if (ti.slot < 0 || ti.slot >= n_slots) {      // expert not resident: caller error
           if (status) atomicExch(status, 2);
           ti.slot = 0;
@@ -268,6 +273,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (read_tile(tile_table, dense_rows, slot_of_expert, tile / n_ntiles).slot == kSlotSkip) continue;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * kBlockN;
@@ -299,6 +305,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int m_tile = tile / n_ntiles, n_tile = tile - m_tile * n_ntiles;
       const TileInfo ti = read_tile(tile_table, dense_rows, slot_of_expert, m_tile);
+      if (ti.slot == kSlotSkip) continue;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = ti.row_begin + row_in_tile;
