@@ -58,6 +58,15 @@ const char *sb_last_error_string(void);
 /* Number of SMs of the current device (grid sizing on the host side). */
 int32_t sb_device_sm_count(void);
 
+/* Rows per tile of the tile tables this library writes and consumes (128 with
+ * the single-CTA grouped GEMM, 256 with the CTA-pair kernel), and whether the
+ * gate/up slab `w13` is expected with gate and up rows interleaved
+ * (row 2j = gate_j, row 2j+1 = up_j) instead of stacked (I gate rows, then I
+ * up rows).  Both follow the kernel choice made once per process through the
+ * environment variable SPARSE_B200_GEMM (pair | single). */
+int32_t sb_tile_rows(void);
+int32_t sb_w13_interleaved(void);
+
 /*
  * Router: logits = x . Wg^T (+ bias) rounded to the model dtype, softmax in
  * fp32, top-k (larger probability first, then smaller expert id), optional

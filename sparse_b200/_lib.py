@@ -43,6 +43,8 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_last_error_string": (C.c_char_p, []),
     "sb_device_sm_count": (i32, []),
     "sb_last_launch_count": (i32, []),
+    "sb_tile_rows": (i32, []),
+    "sb_w13_interleaved": (i32, []),
     "sb_router_topk": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
     "sb_softmax_topk": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "sb_permute_workspace_bytes": (sz, [i32, i32]),

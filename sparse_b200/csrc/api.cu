@@ -2,6 +2,7 @@
 // whole-layer driver and the cache-slot copy.  Declarations and the reference
 // spans they replace are in include/sparse_b200.h.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "sb_common.cuh"
@@ -28,6 +29,17 @@ void count_launch(int n) { g_launches += n; }
 void reset_launch_count() { g_launches = 0; }
 
 static inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, int dense_rows,
+                                  const void *w13, const void *w2, const int32_t *slot_of_expert,
+                                  const void *row_scale, int R_cap, int H, int I, int S, void *hbuf,
+                                  void *out, int32_t *status, cudaStream_t stream) {
+  if (sb_w13_interleaved())
+    return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
+                                      R_cap, H, I, S, hbuf, out, status, stream);
+  return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
+                               H, I, S, hbuf, out, status, stream);
+}
 
 // Carves the caller's workspace; the same walk gives the required size.
 struct LayerScratch {
@@ -70,6 +82,21 @@ using namespace sb;
 extern "C" {
 
 int32_t sb_abi_version(void) { return 1; }
+
+// Which grouped-GEMM kernel this process uses: the CTA-pair kernel
+// (SPARSE_B200_GEMM=pair) or the single-CTA kernel (=single).  Read once.
+static int gemm_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char *v = getenv("SPARSE_B200_GEMM");
+    mode = (v != nullptr && strcmp(v, "single") == 0) ? 0 : 1;   // default: CTA-pair kernel
+  }
+  return mode;
+}
+
+int32_t sb_tile_rows(void) { return gemm_mode() == 1 ? 256 : SB_TILE_M; }
+
+int32_t sb_w13_interleaved(void) { return gemm_mode() == 1 ? 1 : 0; }
 
 const char *sb_last_error_string(void) { return g_err; }
 
@@ -114,8 +141,8 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table, int32_t d
                           const void *w13, const void *w2, const int32_t *slot_of_expert,
                           const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
                           void *hbuf, void *out, int32_t *status, void *stream) {
-  return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
-                               R_cap, H, I, S, hbuf, out, status, static_cast<cudaStream_t>(stream));
+  return launch_grouped_swiglu_any(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
+                                   R_cap, H, I, S, hbuf, out, status, static_cast<cudaStream_t>(stream));
 }
 
 int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
@@ -177,11 +204,11 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
                       s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
                       s.tile_table, stream);
   if (rc != SB_OK) return rc;
-  rc = launch_grouped_swiglu(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
+  rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
                              s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
   if (rc != SB_OK) return rc;
   if (Is > 0) {
-    rc = launch_grouped_swiglu(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
+    rc = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
                                L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
                                s.shared_out, status, stream);
     if (rc != SB_OK) return rc;

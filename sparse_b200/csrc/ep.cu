@@ -89,7 +89,7 @@ __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epo
 //   recv_offsets[E+1], tile table: this rank's receive-side expert segments
 __global__ void __launch_bounds__(256)
 ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict__ owner, int E,
-               int rank, int ep, int tile_cap, int32_t *__restrict__ dst_base,
+               int rank, int ep, int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
                int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table) {
   __shared__ int tot[kMaxExperts];        // items of expert e over all sources
   __shared__ int before_me[kMaxExperts];  // items of expert e from sources < rank
@@ -120,12 +120,12 @@ ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict
       const bool mine = owner[e] == rank;
       my_off[e] = mine ? seg_begin[e] : last;
       tile_start[e] = ts;
-      if (mine) { last = seg_begin[e] + tot[e]; ts += (tot[e] + SB_TILE_M - 1) / SB_TILE_M; }
+      if (mine) { last = seg_begin[e] + tot[e]; ts += (tot[e] + tile_rows - 1) / tile_rows; }
     }
     my_off[E] = last; tile_start[E] = ts;
     tile_table[0] = ts < tile_cap ? ts : tile_cap;
     tile_table[1] = last;
-    tile_table[2] = 0; tile_table[3] = 0;
+    tile_table[2] = tile_rows; tile_table[3] = 0;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) dst_base[e] = seg_begin[e] + before_me[e];
@@ -137,8 +137,8 @@ ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict
       const int ti = tile_start[e] + m;
       if (ti >= tile_cap) break;
       int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
-      const int rb = seg_begin[e] + m * SB_TILE_M;
-      const int re = min(seg_begin[e] + tot[e], rb + SB_TILE_M);
+      const int rb = seg_begin[e] + m * tile_rows;
+      const int re = min(seg_begin[e] + tot[e], rb + tile_rows);
       ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
     }
   }
@@ -306,7 +306,8 @@ int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, i
     return fail(SB_E_INVALID_ARG, "sb_ep_plan: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
   const int tile_cap = recv_cap / SB_TILE_M + E;
   ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, owner, E, rank, ep, tile_cap,
-                                                                   dst_base, recv_offsets, tile_table);
+                                                                   sb_tile_rows(), dst_base, recv_offsets,
+                                                                   tile_table);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -1,0 +1,457 @@
+// Grouped bf16 SwiGLU expert MLP, CTA-pair edition (tcgen05 cta_group::2).
+//
+// Same arithmetic and rounding points as grouped_swiglu.cu; different mapping
+// onto the machine, chosen for ragged expert groups:
+//
+//  * operands are swapped: the WEIGHT rows fill the 256-row M dimension of the
+//    MMA (always full), the TOKENS of one expert are the N dimension, which the
+//    tensor core accepts in steps of 16 up to 256.  A group of 3 tokens costs a
+//    16-wide MMA, not a 128-row tile of padding.
+//  * two CTAs of a cluster work on one 256 x N tile (`cta_group::2`): each CTA
+//    loads 128 weight rows and half of the token rows per 64-deep K step
+//    (32 KB instead of 48 KB per CTA for the same flops), the tensor cores read
+//    the token half of the peer through distributed shared memory.  That cuts
+//    L2->SM traffic by a third, which is what capped the single-CTA kernel.
+//  * six 32 KB stages; TMEM holds two 128-lane x 256-column accumulators per CTA.
+//  * pass 1 reads the gate/up slab with gate and up rows interleaved
+//    (row 2j = gate_j, row 2j+1 = up_j), so the two values a SwiGLU output
+//    needs sit in adjacent TMEM lanes = adjacent threads: one shuffle, no
+//    shared-memory exchange.
+//  * TMA loads are plain 2-D/3-D tile loads (`.cta_group::2`, no multicast);
+//    both CTAs signal the leader CTA's "full" barrier; the leader's MMA thread
+//    frees a stage in both CTAs and publishes a finished accumulator to both
+//    CTAs' epilogue warps with `tcgen05.commit ... multicast::cluster`.
+//
+// Roles per CTA (320 threads): warp 0 lane 0 = TMA producer, warp 1 = TMEM
+// owner (and, in the leader CTA, lane 0 = MMA issuer), warps 2-9 = epilogue.
+// All mbarrier waits are bounded (2 s); on expiry the CTA sets an abort flag,
+// reports through `status`, drains, joins the cluster barrier, frees TMEM.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kTileW = 256;          // weight rows per CTA pair (MMA M)
+constexpr int kRowsPerCta = 128;
+constexpr int kMaxN = 256;           // tokens per tile (MMA N), multiple of 16
+constexpr int kBlockK = 64;
+constexpr int kStages = 6;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 320;         // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kABytes = kRowsPerCta * kBlockK * 2;      // 16 KB
+constexpr uint32_t kBBytes = (kMaxN / 2) * kBlockK * 2;      // 16 KB (this CTA's half of the tokens)
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr int kSlotSkip = -2;
+constexpr int kModeSwiglu = 0, kModeScale = 1;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// arrive on a barrier given by its shared::cluster address (may live in the peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = gtime_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (gtime_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+  }
+}
+// Tile loads of a CTA pair: destination in this CTA, completion bytes counted on
+// the barrier at `bar_cluster_addr` (the leader CTA's).
+__device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const CUtensorMap *tm, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const CUtensorMap *tm, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// completion of all MMAs issued so far -> one arrival on the barrier at this
+// shared-memory offset in BOTH CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// D=f32, A=B=bf16, K-major both, M=256 (pair), N given
+__device__ __forceinline__ uint32_t idesc_m256(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
+}
+
+struct Chunk { int slot, tok_begin, tok_end; };
+
+__device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense_rows,
+                                            const int32_t *slot_of_expert, int c) {
+  Chunk t;
+  if (tile_table == nullptr) {
+    t.slot = 0;
+    t.tok_begin = c * kMaxN;
+    t.tok_end = min(dense_rows, t.tok_begin + kMaxN);
+  } else {
+    const int4 e = __ldg(reinterpret_cast<const int4 *>(tile_table + kTileHeaderInts) + c);
+    t.slot = slot_of_expert ? __ldg(slot_of_expert + e.x) : e.x;
+    t.tok_begin = e.y;
+    t.tok_end = e.z;
+  }
+  return t;
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                 const int32_t *__restrict__ tile_table, int dense_rows,
+                 const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
+                 __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
+                 int32_t *__restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_full = smem_base + kStages * kStageBytes;     // kStages  (used in the leader CTA)
+  const uint32_t bar_empty = bar_full + 8 * kStages;               // kStages  (both CTAs)
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;              // 2        (both CTAs)
+  const uint32_t bar_tempty = bar_tfull + 16;                      // 2        (leader CTA)
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_al + kStages * kStageBytes + 8 * (2 * kStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();               // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
+  const int n_chunks = tile_table ? __ldg(tile_table) : (dense_rows + kMaxN - 1) / kMaxN;
+  const int total = n_chunks * n_wtiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 2 * kEpiWarps); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < total; tile += n_pairs) {
+        const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
+        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c);
+        if (ch.slot == kSlotSkip) continue;
+        if (ch.slot < 0 || ch.slot >= n_slots) {
+          if (status) atomicExch(status, 2);
+          ch.slot = 0;
+        }
+        const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
+        const int tok0 = ch.tok_begin + (int)cta * (n >> 1);       // this CTA's half of the tokens
+        const int wrow = wt * kTileW + (int)cta * kRowsPerCta;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes);
+          tma_pair_load_3d(sa, &tm_w, full_leader, kb * kBlockK, wrow, ch.slot);
+          tma_pair_load_2d(sa + kABytes, &tm_x, full_leader, kb * kBlockK, tok0);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (cta == 0 && lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < total; tile += n_pairs) {
+        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles);
+        if (ch.slot == kSlotSkip) continue;
+        const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
+        const uint32_t idesc = idesc_m256(n);
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * kMaxN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint64_t adesc = umma_desc_sw128(sa);
+          const uint64_t bdesc = umma_desc_sw128(sa + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                             (kb | k) != 0 ? 1u : 0u);
+          tc_commit_pair(bar_empty + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(bar_tfull + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..9, both CTAs) ----------------
+    // Two warps share each quarter of the TMEM lanes (a warp may only read lanes
+    // 32*(warp%4)..+31) and take alternate 32-token chunks, so every scheduler has
+    // two epilogue warps to hide the latency of the dependent math chains.
+    const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int wl = lane_group * 32 + lane;              // weight row inside this CTA's 128
+    const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int tile = pair; tile < total; tile += n_pairs) {
+      const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
+      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c);
+      if (ch.slot == kSlotSkip) continue;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int n_tok = ch.tok_end - ch.tok_begin;
+      const uint32_t taddr = tmem_base + (uint32_t)acc * kMaxN + ((uint32_t)(lane_group * 32) << 16);
+      const int wrow = wt * kTileW + (int)cta * kRowsPerCta + wl;      // row of the weight matrix
+      if (MODE == kModeSwiglu) {
+        // rows are interleaved: even = gate_j, odd = up_j, j = wrow / 2
+        const int feat = wrow >> 1;
+        const bool odd = (wl & 1) != 0;
+        const bool feat_ok = feat < ld_out;
+#pragma unroll 1
+        for (int c0 = half * 32; c0 < n_tok; c0 += 64) {
+          uint32_t v[32];
+          tc_ld32(taddr + c0, v);
+          tc_wait_ld();
+          // The even lane (gate row) finishes the even tokens of the chunk, the odd
+          // lane (up row) the odd ones: each sends the partner the value it will
+          // not use itself.  One shuffle per token pair, no divergent branch.
+          __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0 + (odd ? 1 : 0)) * ld_out + feat;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float keep = round_bf16(__uint_as_float(odd ? v[2 * i + 1] : v[2 * i]));
+            const float give = round_bf16(__uint_as_float(odd ? v[2 * i] : v[2 * i + 1]));
+            const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+            const float g = odd ? got : keep, u = odd ? keep : got;
+            const float s = round_bf16(__fdividef(g, 1.0f + __expf(-g)));
+            const __nv_bfloat16 h = __float2bfloat16_rn(s * u);
+            if (feat_ok && c0 + 2 * i + (odd ? 1 : 0) < n_tok) obase[(size_t)(2 * i) * ld_out] = h;
+          }
+        }
+      } else {
+        const bool col_ok = wrow < ld_out;
+#pragma unroll 1
+        for (int c0 = half * 32; c0 < n_tok; c0 += 64) {
+          uint32_t v[32];
+          tc_ld32(taddr + c0, v);
+          tc_wait_ld();
+          // this lane's route weight of token c0+lane; handed round by shuffle
+          float my_scale = 1.0f;
+          if (row_scale != nullptr && c0 + lane < n_tok)
+            my_scale = __bfloat162float(row_scale[ch.tok_begin + c0 + lane]);
+          __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float sc = __shfl_sync(0xffffffffu, my_scale, j);
+            const float y = round_bf16(__uint_as_float(v[j])) * sc;
+            if (col_ok && c0 + j < n_tok) obase[(size_t)j * ld_out] = __float2bfloat16_rn(y);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && status) atomicExch(status, 1);
+    const unsigned long long t0 = gtime_ns();
+    while (gtime_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();            // neither CTA leaves while the other may still touch its shared memory
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SB_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)kRowsPerCta, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = d2 > 0 ? 3 : 2;
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SB_E_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  return SB_OK;
+}
+
+template <int MODE>
+int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const int32_t *tile_table, int dense_rows,
+                    const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
+                    int num_kb, int n_slots, int32_t *status, int grid, cudaStream_t stream) {
+  auto kern = pair_gemm_kernel<MODE>;
+  SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x, tile_table, dense_rows, slot_of_expert,
+                                              static_cast<const __nv_bfloat16 *>(row_scale),
+                                              static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
+                                              status);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+}  // namespace
+
+// w13 must be in the INTERLEAVED row order (row 2j = gate_j, row 2j+1 = up_j);
+// tile_table must have been built with 256-row tiles.
+int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
+                                   const void *w2, const int32_t *slot_of_expert, const void *row_scale,
+                                   int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
+                                   cudaStream_t stream) {
+  if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
+    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
+  if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
+  if (tile_table == nullptr && (dense_rows < 0 || dense_rows > R_cap))
+    return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: dense_rows=%d outside [0,%d]", dense_rows, R_cap);
+  if (tile_table == nullptr && dense_rows == 0) return SB_OK;
+  if (!rows || !w13 || !w2 || !hbuf || !out) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
+  if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || !aligned(out, 16))
+    return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
+  CUtensorMap tm_x, tm_w13, tm_h, tm_w2;
+  int32_t rc;
+  if ((rc = make_map(&tm_x, rows, (uint64_t)H, (uint64_t)R_cap, 0, "rows")) != SB_OK) return rc;
+  if ((rc = make_map(&tm_w13, w13, (uint64_t)H, (uint64_t)2 * I, (uint64_t)S, "w13")) != SB_OK) return rc;
+  if ((rc = make_map(&tm_h, hbuf, (uint64_t)I, (uint64_t)R_cap, 0, "hbuf")) != SB_OK) return rc;
+  if ((rc = make_map(&tm_w2, w2, (uint64_t)I, (uint64_t)H, (uint64_t)S, "w2")) != SB_OK) return rc;
+  const int grid = (sb_device_sm_count() / 2) * 2;
+  if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
+  rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
+                                H / kBlockK, S, status, grid, stream);
+  if (rc != SB_OK) return rc;
+  return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
+                                 I / kBlockK, S, status, grid, stream);
+}
+
+}  // namespace sb

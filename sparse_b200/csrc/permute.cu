@@ -46,7 +46,7 @@ permute_count_kernel(const int32_t *__restrict__ item_expert, int n_items, int E
 
 // One CTA.  counts[c][e] becomes the number of items of expert e in chunks < c.
 __global__ void __launch_bounds__(1024)
-permute_scan_kernel(int32_t *__restrict__ counts, int nchunks, int E, int tile_cap,
+permute_scan_kernel(int32_t *__restrict__ counts, int nchunks, int E, int tile_cap, int tile_rows,
                     int32_t *__restrict__ expert_offsets, int32_t *__restrict__ tile_table) {
   __shared__ int total[kMaxExperts];
   __shared__ int offs[kMaxExperts + 1];
@@ -74,12 +74,12 @@ permute_scan_kernel(int32_t *__restrict__ counts, int nchunks, int E, int tile_c
     for (int e = 0; e < E; ++e) {
       offs[e] = o; tile_start[e] = ts;
       o += total[e];
-      ts += (total[e] + SB_TILE_M - 1) / SB_TILE_M;
+      ts += (total[e] + tile_rows - 1) / tile_rows;
     }
     offs[E] = o; tile_start[E] = ts;
     tile_table[0] = ts < tile_cap ? ts : tile_cap;
     tile_table[1] = o;          // total rows
-    tile_table[2] = 0; tile_table[3] = 0;
+    tile_table[2] = tile_rows; tile_table[3] = 0;
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) expert_offsets[e] = offs[e];
@@ -89,8 +89,8 @@ permute_scan_kernel(int32_t *__restrict__ counts, int nchunks, int E, int tile_c
       int ti = tile_start[e] + m;
       if (ti >= tile_cap) break;
       int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
-      int rb = offs[e] + m * SB_TILE_M;
-      int re = offs[e + 1] < rb + SB_TILE_M ? offs[e + 1] : rb + SB_TILE_M;
+      int rb = offs[e] + m * tile_rows;
+      int re = offs[e + 1] < rb + tile_rows ? offs[e + 1] : rb + tile_rows;
       ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
     }
   }
@@ -182,7 +182,7 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
                                                                     nchunks, counts);
     SB_LAUNCH_CHECK();
   }
-  permute_scan_kernel<<<1, 1024, 0, stream>>>(counts, nchunks, E, tile_cap, expert_offsets,
+  permute_scan_kernel<<<1, 1024, 0, stream>>>(counts, nchunks, E, tile_cap, sb_tile_rows(), expert_offsets,
                                               tile_table);
   SB_LAUNCH_CHECK();
   if (nchunks > 0) {

@@ -75,6 +75,10 @@ int32_t launch_grouped_swiglu(const void *rows, const int32_t *tile_table, int d
                               const void *w13, const void *w2, const int32_t *slot_of_expert,
                               const void *row_scale, int R_cap, int H, int I, int S,
                               void *hbuf, void *out, int32_t *status, cudaStream_t stream);
+int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows,
+                                   const void *w13, const void *w2, const int32_t *slot_of_expert,
+                                   const void *row_scale, int R_cap, int H, int I, int S,
+                                   void *hbuf, void *out, int32_t *status, cudaStream_t stream);
 int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
                        const void *shared_out, int T, int H, int K, void *out,
                        cudaStream_t stream);

@@ -20,6 +20,22 @@ from . import _lib
 from ._lib import lib, check, MoeLayer
 
 
+def pack_w13(gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gate and up matrices [I,H] -> one slab entry [2I,H] in the row order the
+    loaded library expects: stacked (gate rows, then up rows) for the single-CTA
+    GEMM, interleaved (g0,u0,g1,u1,...) for the CTA-pair GEMM."""
+    i, h = gate.shape
+    if out is None:
+        out = torch.empty((2 * i, h), dtype=torch.bfloat16, device=gate.device)
+    if lib.sb_w13_interleaved():
+        out[0::2].copy_(gate)
+        out[1::2].copy_(up)
+    else:
+        out[:i].copy_(gate)
+        out[i:].copy_(up)
+    return out
+
+
 class LayerWeights:
     """Weights of one MoE layer on one GPU."""
 
@@ -50,9 +66,7 @@ class LayerWeights:
 
     def set_shared(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
                    scalar_gate: Optional[torch.Tensor]) -> None:
-        i = self.shared_inter
-        self.shared_w13[0, :i].copy_(gate)
-        self.shared_w13[0, i:].copy_(up)
+        pack_w13(gate, up, self.shared_w13[0])
         self.shared_w2[0].copy_(down)
         self.shared_gate_w = None
         if scalar_gate is not None:
@@ -60,9 +74,7 @@ class LayerWeights:
 
     def load_expert(self, slot: int, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
         """Synchronous (setup-time) load of one expert's three matrices into a slot."""
-        i = self.inter
-        self.w13[slot, :i].copy_(gate)
-        self.w13[slot, i:].copy_(up)
+        pack_w13(gate, up, self.w13[slot])
         self.w2[slot].copy_(down)
 
     def set_slot_map(self, slot_of_expert: Sequence[int]) -> None:

@@ -26,7 +26,7 @@ from .cache import ExpertWeightCache, SlotPool
 from .config import BlockConfig
 from .context import Metrics, SparseContext
 from .epipe import EpipePlan, RollingGate, plan_residual_scan, plan_upfront_scan
-from .layer import LayerWeights
+from .layer import LayerWeights, pack_w13
 
 SLOT_SKIP = -2      # slot_of_expert value: not part of this GEMM launch
 SLOT_ABSENT = -1    # slot_of_expert value: not resident (routing to it is an error)
@@ -41,7 +41,7 @@ class HostExperts:
         self.w2: Dict[int, torch.Tensor] = {}
 
     def add(self, expert: int, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, pin: bool = True) -> None:
-        w13 = torch.cat([gate, up], 0).to(torch.bfloat16).contiguous()
+        w13 = pack_w13(gate.to(torch.bfloat16), up.to(torch.bfloat16)).contiguous()
         w2 = down.to(torch.bfloat16).contiguous()
         if pin and torch.cuda.is_available():
             w13, w2 = w13.pin_memory(), w2.pin_memory()

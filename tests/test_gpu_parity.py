@@ -10,6 +10,7 @@ import torch
 from conftest import block_weights, load_golden, rel_l2
 from oracle import moe_oracle as mo
 from sparse_b200 import synth
+from sparse_b200.layer import pack_w13
 
 pytestmark = pytest.mark.gpu
 
@@ -144,13 +145,15 @@ def test_permute_exact(n_tok, k, e, h):
     assert torch.equal(p.item_of_slot.cpu().long()[:n], item_of_slot)
     assert torch.equal(p.rows.cpu()[:n], x[item_of_slot // k])
     assert torch.equal(p.slot_scale.cpu()[:n], wts.reshape(-1)[item_of_slot])
+    from sparse_b200._lib import lib
+    tile_rows = lib.sb_tile_rows()
     tt = p.tile_table.cpu()
     n_tiles = int(tt[0])
     ent = tt[4:4 + 4 * n_tiles].view(-1, 4)
     want = []
     for ee in range(e):
-        for rb in range(int(offs[ee]), int(offs[ee + 1]), 128):
-            want.append([ee, rb, min(rb + 128, int(offs[ee + 1])), 0])
+        for rb in range(int(offs[ee]), int(offs[ee + 1]), tile_rows):
+            want.append([ee, rb, min(rb + tile_rows, int(offs[ee + 1])), 0])
     assert ent.tolist() == want
     assert int(tt[1]) == n
 
@@ -201,7 +204,7 @@ def test_grouped_swiglu_against_oracle(h, i, e, counts):
     x = torch.randn(n, h).to(bf)
     scale = torch.rand(n).to(bf)
     p = ops.permute(x.to(dev()), ids.to(dev()), e, 1, item_scale=scale.to(dev()))
-    w13 = torch.stack([torch.cat([gate[ee], up[ee]]) for ee in range(e)]).to(dev())
+    w13 = torch.stack([pack_w13(gate[ee], up[ee]) for ee in range(e)]).to(dev())
     w2 = torch.stack(down).to(dev())
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     out, hid = ops.grouped_swiglu(p.rows, w13, w2, tile_table=p.tile_table, row_scale=p.slot_scale,
@@ -225,7 +228,7 @@ def test_dense_swiglu_shared_expert_shape():
     h, i, t = 256, 320, 200
     g, u, d = [(torch.randn(*s) * 0.05).to(bf) for s in ((i, h), (i, h), (h, i))]
     x = torch.randn(t, h).to(bf)
-    w13 = torch.cat([g, u]).unsqueeze(0).to(dev())
+    w13 = pack_w13(g, u).unsqueeze(0).to(dev())
     out, _ = ops.grouped_swiglu(x.to(dev()), w13, d.unsqueeze(0).to(dev()), dense_rows=t)
     want = mo.expert_mlp(x, g, u, d)
     assert rel_l2(out.cpu()[:t], want) < REL_L2
@@ -247,11 +250,11 @@ def test_slot_indirection_and_slab_reuse():
     w13 = torch.zeros(s, 2 * i, h, dtype=bf)
     w2 = torch.zeros(s, h, i, dtype=bf)
     for ee, sl in enumerate(slots):
-        w13[sl] = torch.cat([gate[ee], up[ee]])
+        w13[sl] = pack_w13(gate[ee], up[ee])
         w2[sl] = down[ee]
     out_a, _ = ops.grouped_swiglu(p.rows, w13.to(dev()), w2.to(dev()), tile_table=p.tile_table,
                                   slot_of_expert=torch.tensor(slots, dtype=torch.int32, device=dev()))
-    w13_id = torch.stack([torch.cat([gate[ee], up[ee]]) for ee in range(e)]).to(dev())
+    w13_id = torch.stack([pack_w13(gate[ee], up[ee]) for ee in range(e)]).to(dev())
     out_b, _ = ops.grouped_swiglu(p.rows, w13_id, torch.stack(down).to(dev()), tile_table=p.tile_table)
     assert torch.equal(out_a.cpu()[:300], out_b.cpu()[:300])
 
