@@ -30,8 +30,8 @@ library it happens to run on:
   a stable descending sort gives.  Exact ties only occur with bf16 logits.
 * router accumulation order.  The reference's logits come from a library GEMM
   whose fp32 summation order is unspecified.  `router_logits_fixed_order`
-  defines one (32 partial sums over interleaved groups of 8 elements, then an
-  xor-butterfly) that the CUDA kernel follows bit for bit;
+  defines one (per lane an even and an odd partial sum over interleaved groups
+  of 8 elements, then an xor-butterfly) that the CUDA kernel follows bit for bit;
   `router_logits_library` is the reference's literal `F.linear` call.  The two
   differ only by rare 1-ulp roundings of a logit.
 """
@@ -59,23 +59,25 @@ def _fixed_order_dot(xf: np.ndarray, wf: np.ndarray) -> np.ndarray:
     """fp32 dot products of every row of xf [T,H] with every row of wf [R,H]
     in the summation order the CUDA router kernel uses.
 
-    The H elements are cut into groups of 8.  Partial sum `l` (0..31) takes
-    groups l, l+32, l+64, ... in increasing order and, inside a group, elements
-    0..7 in order, each step `acc = fl(acc + fl(x*w))`.  The 32 partial sums are
-    then combined by an xor-butterfly with offsets 16, 8, 4, 2, 1."""
+    The H elements are cut into groups of 8.  Lane `l` (0..31) takes groups
+    l, l+32, l+64, ... in increasing order and keeps two partial sums, one over
+    the even and one over the odd elements of its groups, each step
+    `p = fl(p + fl(x*w))`; its lane sum is `fl(p_even + p_odd)`.  The 32 lane
+    sums are then combined by an xor-butterfly with offsets 16, 8, 4, 2, 1."""
     t, h = xf.shape
     r = wf.shape[0]
     assert h % 8 == 0
     groups = h // 8
-    acc = np.zeros((t, r, 32), dtype=np.float32)
+    part = np.zeros((2, t, r, 32), dtype=np.float32)
     steps = (groups + 31) // 32
     for j in range(steps):
         nl = min(32, groups - j * 32)
         base = (j * 32 + np.arange(nl)) * 8
         for i in range(8):
             cols = base + i
-            prod = xf[:, None, cols] * wf[None, :, cols]      # fl(x*w)
-            acc[:, :, :nl] = acc[:, :, :nl] + prod            # fl(acc + .)
+            prod = xf[:, None, cols] * wf[None, :, cols]                  # fl(x*w)
+            part[i & 1][:, :, :nl] = part[i & 1][:, :, :nl] + prod        # fl(p + .)
+    acc = part[0] + part[1]
     lanes = np.arange(32)
     for off in (16, 8, 4, 2, 1):
         acc = acc + acc[:, :, lanes ^ off]

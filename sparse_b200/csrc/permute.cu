@@ -132,6 +132,105 @@ permute_scatter_kernel(const int32_t *__restrict__ item_expert,
   }
 }
 
+// Count, scan and scatter in ONE CTA for up to kFusedMaxItems items (a 4096-token
+// batch with top-4 routing is 16384): each of the 32 warps owns a contiguous
+// range of items, histograms it in shared memory, the per-expert prefix over the
+// warps gives every range its base, and the same warp then ranks its items in
+// order.  Same result as the three-kernel path, two launches and their
+// scheduling gaps fewer; the workspace is not touched.
+constexpr int kFusedMaxItems = 32768;
+
+__global__ void __launch_bounds__(1024)
+permute_fused_kernel(const int32_t *__restrict__ item_expert, const __nv_bfloat16 *__restrict__ item_scale,
+                     int n_items, int E, int tile_cap, int tile_rows, int32_t *__restrict__ expert_offsets,
+                     int32_t *__restrict__ slot_of_item, int32_t *__restrict__ item_of_slot,
+                     __nv_bfloat16 *__restrict__ slot_scale, int32_t *__restrict__ tile_table) {
+  extern __shared__ int fused_smem[];
+  int *hist = fused_smem;                    // [32][E] counts, then bases
+  int *offs = hist + 32 * E;                 // [E+1]
+  int *tile_start = offs + (E + 1);          // [E+1]
+  int *tot = tile_start + (E + 1);           // [E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_warp = ((n_items + 31) / 32 + 31) & ~31;     // items per warp, multiple of 32
+  const int begin = warp * per_warp;
+  const int end = min(n_items, begin + per_warp);
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  for (int i = begin + lane; i < end; i += 32) {
+    const int e = item_expert[i];
+    if (e >= 0 && e < E) atomicAdd(&hist[warp * E + e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) { const int c = hist[w * E + e]; hist[w * E + e] = run; run += c; }
+    tot[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, ts = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = o; tile_start[e] = ts;
+      o += tot[e];
+      ts += (tot[e] + tile_rows - 1) / tile_rows;
+    }
+    offs[E] = o; tile_start[E] = ts;
+    tile_table[0] = ts < tile_cap ? ts : tile_cap;
+    tile_table[1] = o;
+    tile_table[2] = tile_rows; tile_table[3] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) expert_offsets[e] = offs[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int nt = tile_start[e + 1] - tile_start[e];
+    for (int m = 0; m < nt; ++m) {
+      const int ti = tile_start[e] + m;
+      if (ti >= tile_cap) break;
+      int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
+      const int rb = offs[e] + m * tile_rows;
+      const int re = offs[e + 1] < rb + tile_rows ? offs[e + 1] : rb + tile_rows;
+      ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
+    }
+  }
+  // scatter: hist[warp][e] is now the number of items of e in earlier warps.
+  // Items are fetched eight rounds ahead so the loads overlap instead of each
+  // round waiting for its own.
+  constexpr int kBatch = 8;
+  for (int b0 = begin; b0 < end; b0 += 32 * kBatch) {
+    int ev[kBatch];
+    __nv_bfloat16 sv[kBatch];
+#pragma unroll
+    for (int r = 0; r < kBatch; ++r) {
+      const int i = b0 + r * 32 + lane;
+      ev[r] = -1;
+      if (i < end) {
+        ev[r] = item_expert[i];
+        if (slot_scale != nullptr) sv[r] = item_scale[i];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kBatch; ++r) {
+      const int i = b0 + r * 32 + lane;
+      int e = ev[r];
+      if (e < 0 || e >= E) e = -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      int slot = -1;
+      if (e >= 0) slot = offs[e] + hist[warp * E + e] + rank;
+      __syncwarp();
+      if (e >= 0 && rank == 0) hist[warp * E + e] += __popc(peers);
+      __syncwarp();
+      if (i < end) {
+        slot_of_item[i] = slot;
+        if (slot >= 0) {
+          item_of_slot[slot] = i;
+          if (slot_scale != nullptr) slot_scale[slot] = sv[r];
+        }
+      }
+    }
+  }
+}
+
 // One warp per output row.
 __global__ void __launch_bounds__(256)
 permute_gather_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item_of_slot,
@@ -176,6 +275,26 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
   const int nchunks = num_chunks(n_items);
   int32_t *counts = static_cast<int32_t *>(ws);
   const int tile_cap = n_items / SB_TILE_M + E;
+  if (n_items > 0 && n_items <= kFusedMaxItems) {
+    const size_t smem = ((size_t)32 * E + 2 * (size_t)(E + 1) + E) * sizeof(int);
+    if (smem > 48 * 1024)
+      SB_CUDA_CHECK(cudaFuncSetAttribute(permute_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    permute_fused_kernel<<<1, 1024, smem, stream>>>(
+        item_expert, static_cast<const __nv_bfloat16 *>(item_scale), n_items, E, tile_cap, sb_tile_rows(),
+        expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale), tile_table);
+    SB_LAUNCH_CHECK();
+    if (out_rows != nullptr) {
+      int gblocks = (n_items + 7) / 8;
+      const int max_blocks = sb_device_sm_count() * 8;
+      if (gblocks > max_blocks) gblocks = max_blocks;
+      permute_gather_kernel<<<gblocks, 256, 0, stream>>>(
+          static_cast<const uint4 *>(x), item_of_slot, expert_offsets, E, items_per_row, H / 8,
+          static_cast<uint4 *>(out_rows));
+      SB_LAUNCH_CHECK();
+    }
+    return SB_OK;
+  }
   if (nchunks > 0) {
     int blocks = (nchunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
     permute_count_kernel<<<blocks, kWarpsPerBlock * 32, 0, stream>>>(item_expert, n_items, E,

@@ -5,12 +5,13 @@
 // (utils/eval_core.py:9461-9462).
 //
 // Summation order of one logit (bit-exact contract with the CPU oracle): the H
-// inputs are cut into groups of 8; lane l of a warp accumulates groups
-// l, l+32, l+64, ... in increasing order, elements 0..7 of a group in order,
-// each step acc = fl(acc + fl(x*w)) (for bf16 inputs the product is exact, so a
-// fused multiply-add gives the same bits); the 32 lane sums are combined by an
-// xor-butterfly with offsets 16, 8, 4, 2, 1; the bias is added in fp32 and the
-// result is rounded once to the model dtype.
+// inputs are cut into groups of 8; lane l of a warp takes groups l, l+32, l+64,
+// ... in increasing order and keeps two partial sums, one over the even and one
+// over the odd elements of its groups, elements in increasing order, each step
+// p = fl(p + fl(x*w)) (for bf16 inputs the product is exact, so a fused
+// multiply-add gives the same bits); the lane sum is fl(p_even + p_odd); the 32
+// lane sums are combined by an xor-butterfly with offsets 16, 8, 4, 2, 1; the
+// bias is added in fp32 and the result is rounded once to the model dtype.
 //
 // Work split: one CTA owns TB tokens whose activations sit in shared memory;
 // each of its 8 warps streams pairs of router rows from L2 and dots them with
@@ -145,12 +146,59 @@ __device__ void warp_softmax_topk(const float *lg, int E, int K, int renorm, int
   }
 }
 
+// Two running partial sums (even / odd elements) packed for the two-wide FMA.
+struct Acc2 {
+  unsigned long long v;
+  __device__ static Acc2 zero() { Acc2 a; a.v = 0ull; return a; }
+  __device__ float lane_sum() const {
+    return __fadd_rn(__uint_as_float((uint32_t)v), __uint_as_float((uint32_t)(v >> 32)));
+  }
+  template <typename P> __device__ void fma(const P &x, const P &w, int i) { x.fma_into(v, w, i); }
+};
+
+// Eight consecutive elements as four (even, odd) pairs.
+template <typename IN> struct Pair4;
+
+template <> struct Pair4<__nv_bfloat16> {
+  unsigned long long p[4];
+  __device__ static unsigned long long widen(uint32_t word) {      // bf16x2 -> {f32 lo, f32 hi}
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(word << 16), "r"(word & 0xffff0000u));
+    return r;
+  }
+  __device__ void load(const uint4 *src) {
+    const uint4 q = *src;
+    p[0] = widen(q.x); p[1] = widen(q.y); p[2] = widen(q.z); p[3] = widen(q.w);
+  }
+  // products of bf16 values are exact in fp32, so the fused form equals mul-then-add
+  __device__ void fma_into(unsigned long long &acc, const Pair4 &w, int i) const {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(p[i]), "l"(w.p[i]));
+  }
+};
+
+template <> struct Pair4<float> {
+  float e[8];
+  __device__ void load(const uint4 *src) {
+    const uint4 a = src[0], b = src[1];
+    e[0] = __uint_as_float(a.x); e[1] = __uint_as_float(a.y); e[2] = __uint_as_float(a.z);
+    e[3] = __uint_as_float(a.w); e[4] = __uint_as_float(b.x); e[5] = __uint_as_float(b.y);
+    e[6] = __uint_as_float(b.z); e[7] = __uint_as_float(b.w);
+  }
+  // fp32 inputs: multiply and add round separately (the order the CPU check emulates)
+  __device__ void fma_into(unsigned long long &acc, const Pair4 &w, int i) const {
+    float lo = __uint_as_float((uint32_t)acc), hi = __uint_as_float((uint32_t)(acc >> 32));
+    lo = __fadd_rn(lo, __fmul_rn(e[2 * i], w.e[2 * i]));
+    hi = __fadd_rn(hi, __fmul_rn(e[2 * i + 1], w.e[2 * i + 1]));
+    acc = ((unsigned long long)__float_as_uint(hi) << 32) | (unsigned long long)__float_as_uint(lo);
+  }
+};
+
 template <typename IN, int TB>
-__global__ void __launch_bounds__(kRouterThreads)
+__global__ void __launch_bounds__(kRouterThreads, 2)
 router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *__restrict__ bias,
               const IN *__restrict__ wsg, int T, int H, int E, int K, int renorm, int fp32_logits,
-              int32_t *__restrict__ out_idx, IN *__restrict__ out_w, void *__restrict__ out_logits,
-              IN *__restrict__ out_shared) {
+              int tb_eff, int32_t *__restrict__ out_idx, IN *__restrict__ out_w,
+              void *__restrict__ out_logits, IN *__restrict__ out_shared) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kVecPerGroup = sizeof(IN) == 2 ? 1 : 2;      // uint4 per 8 elements
   const int G = H / 8;
@@ -159,11 +207,11 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
   const int NR = E + (wsg != nullptr ? 1 : 0);
   const int ldl = E + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * TB;
+  const int t0 = blockIdx.x * tb_eff;      // this CTA's tokens: t0 .. t0 + tb_eff - 1 (tb_eff <= TB)
 
   // stage the activation tile
   const int vec_per_tok = G * kVecPerGroup;
-  for (int i = threadIdx.x; i < TB * vec_per_tok; i += kRouterThreads) {
+  for (int i = threadIdx.x; i < tb_eff * vec_per_tok; i += kRouterThreads) {
     int t = i / vec_per_tok, v = i - t * vec_per_tok;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (t0 + t < T)
@@ -172,58 +220,87 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
   }
   __syncthreads();
 
+  // Four router rows per warp pass: one shared-memory read of a token's 8
+  // activations feeds 32 multiply-adds, issued as 16 two-wide fp32 FMAs
+  // (`fma.rn.f32x2`: two independent IEEE FMAs per instruction, so the bits are
+  // those of scalar FMAs).  Each lane therefore keeps TWO partial sums per logit,
+  // one over the even and one over the odd elements of its groups.  The next
+  // step's weight vectors are fetched before the current step's math.
+  constexpr int RW = 4;
   const int steps = (G + 31) / 32;
-  const int pairs = (NR + 1) / 2;
-  for (int pr = warp; pr < pairs; pr += kRouterWarps) {
-    const int r0 = 2 * pr, r1 = 2 * pr + 1;
-    const IN *w0 = (r0 < E) ? wg + (size_t)r0 * H : wsg;
-    const IN *w1 = (r1 < E) ? wg + (size_t)r1 * H : ((r1 < NR) ? wsg : nullptr);
-    float acc[TB][2];
+  const int groups = (NR + RW - 1) / RW;
+  for (int grp = warp; grp < groups; grp += kRouterWarps) {
+    const IN *wp[RW];
 #pragma unroll
-    for (int t = 0; t < TB; ++t) { acc[t][0] = 0.f; acc[t][1] = 0.f; }
+    for (int r = 0; r < RW; ++r) {
+      const int row = grp * RW + r;
+      wp[r] = (row < E) ? wg + (size_t)row * H : ((row < NR) ? wsg : nullptr);
+    }
+    Acc2 acc[TB][RW];
+#pragma unroll
+    for (int t = 0; t < TB; ++t)
+#pragma unroll
+      for (int r = 0; r < RW; ++r) acc[t][r] = Acc2::zero();
+    uint4 cur[RW][kVecPerGroup], nxt[RW][kVecPerGroup];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+      for (int v = 0; v < kVecPerGroup; ++v) {
+        cur[r][v] = make_uint4(0, 0, 0, 0);
+        if (lane < G && wp[r] != nullptr)
+          cur[r][v] = __ldg(reinterpret_cast<const uint4 *>(wp[r] + (size_t)lane * 8) + v);
+      }
     for (int j = 0; j < steps; ++j) {
       const int g = j * 32 + lane;
-      if (g < G) {
-        float a[8], b[8];
-        Load8<IN>::from_global(w0, (size_t)g * 8, a);
-        if (w1 != nullptr) Load8<IN>::from_global(w1, (size_t)g * 8, b);
-        else {
+      const int gn = g + 32;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) b[i] = 0.f;
+      for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int v = 0; v < kVecPerGroup; ++v) {
+          nxt[r][v] = make_uint4(0, 0, 0, 0);
+          if (gn < G && wp[r] != nullptr)
+            nxt[r][v] = __ldg(reinterpret_cast<const uint4 *>(wp[r] + (size_t)gn * 8) + v);
         }
+      if (g < G) {
+        Pair4<IN> w[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) w[r].load(&cur[r][0]);
 #pragma unroll
         for (int t = 0; t < TB; ++t) {
-          float xv[8];
-          Load8<IN>::from(sx + ((size_t)t * G + g) * kVecPerGroup, xv);
+          if (t < tb_eff) {
+            Pair4<IN> xv;
+            xv.load(sx + ((size_t)t * G + g) * kVecPerGroup);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (Load8<IN>::kExactProduct) {
-              acc[t][0] = __fmaf_rn(xv[i], a[i], acc[t][0]);
-              acc[t][1] = __fmaf_rn(xv[i], b[i], acc[t][1]);
-            } else {
-              acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(xv[i], a[i]));
-              acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(xv[i], b[i]));
-            }
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int r = 0; r < RW; ++r) acc[t][r].fma(xv, w[r], i);
           }
         }
       }
+#pragma unroll
+      for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int v = 0; v < kVecPerGroup; ++v) cur[r][v] = nxt[r][v];
     }
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
-      float s0 = butterfly_sum(acc[t][0]);
-      float s1 = butterfly_sum(acc[t][1]);
-      if (lane == 0) {
-        if (r0 < E && bias != nullptr) s0 = __fadd_rn(s0, bias[r0]);
-        if (r1 < E && bias != nullptr) s1 = __fadd_rn(s1, bias[r1]);
-        // the shared gate's logit (row E) is always a model-dtype linear output
-        slog[t * ldl + r0] = (fp32_logits && r0 < E) ? s0 : Load8<IN>::round_model(s0);
-        if (r1 < NR) slog[t * ldl + r1] = (fp32_logits && r1 < E) ? s1 : Load8<IN>::round_model(s1);
+      if (t < tb_eff) {
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+          const int row = grp * RW + r;
+          float sum = butterfly_sum(acc[t][r].lane_sum());
+          if (lane == 0 && row < NR) {
+            if (row < E && bias != nullptr) sum = __fadd_rn(sum, bias[row]);
+            // the shared gate's logit (row E) is always a model-dtype linear output
+            slog[t * ldl + row] = (fp32_logits && row < E) ? sum : Load8<IN>::round_model(sum);
+          }
+        }
       }
     }
   }
   __syncthreads();
 
-  for (int t = warp; t < TB; t += kRouterWarps) {
+  for (int t = warp; t < tb_eff; t += kRouterWarps) {
     const int tok = t0 + t;
     if (tok >= T) continue;
     const float *lg = slog + t * ldl;
@@ -266,10 +343,16 @@ int32_t launch_router_tb(const void *x, const void *wg, const float *bias, const
   auto kern = router_kernel<IN, TB>;
   if (smem > 48 * 1024)
     SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int blocks = (T + TB - 1) / TB;
+  // tokens per CTA: as few as keeps the grid within four CTAs per SM, so the
+  // last wave is full (4096 tokens on 148 SMs -> 7 per CTA, 586 CTAs)
+  const int slots = 4 * (sb_device_sm_count() > 0 ? sb_device_sm_count() : 148);
+  int tb_eff = (T + slots - 1) / slots;
+  if (tb_eff < 1) tb_eff = 1;
+  if (tb_eff > TB) tb_eff = TB;
+  int blocks = (T + tb_eff - 1) / tb_eff;
   kern<<<blocks, kRouterThreads, smem, stream>>>(
       static_cast<const IN *>(x), static_cast<const IN *>(wg), bias, static_cast<const IN *>(wsg),
-      T, H, E, K, renorm, fp32_logits, out_idx, static_cast<IN *>(out_w), out_logits,
+      T, H, E, K, renorm, fp32_logits, tb_eff, out_idx, static_cast<IN *>(out_w), out_logits,
       static_cast<IN *>(out_shared));
   SB_LAUNCH_CHECK();
   return SB_OK;
@@ -281,9 +364,9 @@ int32_t launch_router_t(const void *x, const void *wg, const float *bias, const 
                         void *out_w, void *out_logits, void *out_shared, cudaStream_t stream) {
   // Fewer tokens per CTA when there are few tokens, so decode-sized calls still
   // spread over the SMs; 16 per CTA at prefill sizes to amortise the weight reads.
-  const size_t tile16 = (size_t)16 * H * sizeof(IN) + 16 * (size_t)(E + 1) * 4;
-  if (T >= 2048 && tile16 <= 200 * 1024)
-    return launch_router_tb<IN, 16>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
+  const size_t tile8 = (size_t)8 * H * sizeof(IN) + 8 * (size_t)(E + 1) * 4;
+  if (T >= 1024 && tile8 <= 100 * 1024)
+    return launch_router_tb<IN, 8>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
                                     out_w, out_logits, out_shared, stream);
   if (T >= 256)
     return launch_router_tb<IN, 4>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,

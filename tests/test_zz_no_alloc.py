@@ -66,9 +66,9 @@ def _run_pair(n_tok, k, h, e, seed, dev):
 def test_noalloc_matches_workspace_variant_on_two_calls_in_a_row():
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    _run_pair(n_tok=3000, k=4, h=256, e=60, seed=1, dev=dev)    # larger first ...
+    _run_pair(n_tok=9000, k=4, h=128, e=60, seed=1, dev=dev)    # larger first (beyond the one-CTA path, so the scratch is used) ...
     _run_pair(n_tok=37, k=2, h=64, e=8, seed=2, dev=dev)        # ... then small: stale cells must not matter
-    _run_pair(n_tok=3000, k=4, h=256, e=60, seed=3, dev=dev)
+    _run_pair(n_tok=9000, k=4, h=128, e=60, seed=3, dev=dev)
 
 
 def test_noalloc_refuses_sizes_beyond_its_scratch():
