@@ -195,9 +195,23 @@ def stage_breakdown(lw, shape, xs, steps):
     reps = max(5, min(steps, 50))
 
     def timed(name, fn):
-        for _ in range(3):
-            fn(0)
-        out[name] = _time_region(fn, reps, stream) / reps
+        # Each stage is replayed from a CUDA graph of 4 calls so that the host side of
+        # the wrappers (allocations, ctypes) cannot stretch the device time of the
+        # short kernels.
+        for j in range(3):
+            fn(j)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for j in range(4):
+                    fn(j)
+        stream.wait_stream(side)
+        torch.cuda.synchronize()
+        graph.replay()
+        out[name] = _time_region(lambda i: graph.replay(), reps, stream) / (reps * 4)
 
     timed("router_topk", lambda j: ops.router_topk(xs[j % len(xs)], lw.router_w, k, bias=lw.router_bias,
                                                    w_shared_gate=lw.shared_gate_w))
@@ -219,6 +233,46 @@ def stage_breakdown(lw, shape, xs, steps):
         "shared_swiglu": 2 * t * h * 2 * ish + 2 * t * ish * h,
     }
     return out, bytes_, flops, distinct
+
+
+def token_sweep(lw, shape, peaks, counts=(1, 8, 64, 256, 1024)):
+    """Decode-to-prefill sweep of the same layer: device time per pass at small
+    token counts (four passes over rotated inputs captured in one CUDA graph, so
+    launch gaps are what a graph-captured serving step would see), the roofline
+    for the experts actually touched, and tokens/s."""
+    from sparse_b200.layer import LayerRunner
+    from sparse_b200 import synth
+    dev = lw.device
+    out = {}
+    for t in counts:
+        runner = LayerRunner(lw, shape.top_k, t)
+        xs = [synth.make_hidden(t, shape.hidden, seed=50 + b).to(torch.bfloat16).to(dev) for b in range(4)]
+        for b in range(4):
+            runner.forward(xs[b])
+        torch.cuda.synchronize()
+        touched = int(torch.unique(runner.topk_idx[:t]).numel())
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            runner.forward(xs[0])
+            with torch.cuda.graph(graph, stream=side):
+                for b in range(4):
+                    runner.forward(xs[b])
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        reps = 50
+        ms = _time_region(lambda i: graph.replay(), reps, torch.cuda.current_stream(dev)) / (reps * 4)
+        runner.check_status()
+        flops = shape.flops_per_token() * t
+        hbm = touched * shape.routed_expert_bytes_bf16 + 3 * shape.hidden * shape.shared_inter * 2 \
+            + 2 * t * shape.hidden * 2
+        roof = max(flops / (peaks["bf16_tflops"] * 1e12), hbm / (peaks["hbm_gbs"] * 1e9)) * 1e3
+        out[str(t)] = {"ms": ms, "tokens_per_s": t / (ms * 1e-3), "experts_touched": touched,
+                       "roofline_ms": roof, "frac": roof / ms, "launches": runner.last_launches}
+    return out
 
 
 def run_ours(args):
@@ -379,6 +433,8 @@ def run_ours(args):
                                   "distinct_experts": distinct,
                                   "nvlink_bytes_per_gpu_per_direction": nvlink_bytes,
                                   "nvlink_peak": "900 GB/s per direction (datasheet)"}
+        if world == 1 and not args.no_sweep:
+            line["sweep"] = token_sweep(block.weights, shape, peaks)
         if world == 1 and not args.no_cpu_baseline:
             tps, ms, cores = cpu_reference_tokens_per_s(3, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
@@ -397,6 +453,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the decode-to-prefill token sweep")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -196,6 +196,33 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
                           int32_t R_cap, int32_t H, int32_t I, int32_t S,
                           void *hbuf, void *out, int32_t *status, void *stream);
 
+/* Token counts up to this use the weight-streaming kernels below inside
+ * sb_moe_layer_forward instead of the tensor-core grouped GEMM. */
+#define SB_DECODE_MAX_TOKENS 16
+
+/*
+ * Decode-sized expert MLPs (a few tokens against whole expert matrices): the
+ * same arithmetic as sb_grouped_swiglu for the routed groups of `tile_table`
+ * AND the shared expert, as two weight-streaming launches on CUDA cores (one
+ * warp per output feature).  Replaces the same reference spans as
+ * sb_grouped_swiglu (utils/eval_core.py:11767-11793, 11765, 9455-9463) for
+ * S == 1 decode steps.  Routed token rows are read through `item_of_slot`
+ * (row = item / items_per_row of `x`), so sb_permute may be called with
+ * out_rows == NULL.
+ *
+ *   x [T,H]; hbuf [n_items, I]; y [n_items, H]; shared_h [T, I_shared];
+ *   shared_out [T, H]; row_scale [n_items] and shared_scale [T] bf16 or NULL;
+ *   shared_w13 / shared_w2 NULL = no shared expert; tile_table NULL = no
+ *   routed groups.  w13 row order as sb_w13_interleaved() says.
+ * Limits: H, I, I_shared multiples of 8.
+ */
+int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
+                          const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
+                          const void *w2, const void *row_scale, int32_t H, int32_t I, int32_t n_slots,
+                          void *hbuf, void *y, const void *shared_w13, const void *shared_w2,
+                          const void *shared_scale, int32_t I_shared, int32_t T, void *shared_h,
+                          void *shared_out, int32_t *status, void *stream);
+
 /*
  * Un-permute and combine: for each token add its K expert rows in ascending
  * expert id, every add rounding to bf16, then add the shared expert's row.
@@ -261,10 +288,14 @@ int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_
                       int32_t *status, void *stream);
 
 /* From the complete counts matrix: where this rank's items of each expert start
- * in the owner's receive buffer (`dst_base` [E]), and this rank's own
+ * in the destination's receive buffer (`dst_base` [E]), and this rank's own
  * receive-side segments (`recv_offsets` [E+1], tile table as in sb_permute,
- * sized by sb_tile_table_ints(recv_cap, E)).  Receive buffers are laid out by
- * expert id, then source rank, then the source's stable item order. */
+ * sized by sb_tile_table_ints(recv_cap, E)).  `owner` is int32 [ep][E]:
+ * owner[s][e] = rank that executes expert e for tokens on rank s (identical
+ * rows for plain ownership; different rows when experts are replicated, as in
+ * the reference's dest_rank_table, utils/eval_core.py:672-717).  Receive
+ * buffers are laid out by expert id, then source rank, then the source's
+ * stable item order.  sb_ep_dispatch takes row `rank` of the same table. */
 int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, int32_t rank,
                    int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
                    int32_t *tile_table, void *stream);

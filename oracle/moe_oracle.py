@@ -267,7 +267,8 @@ def ep_block_forward(xs: List[torch.Tensor], cw: Dict[str, object], top_k: int,
                      owner: torch.Tensor, norm_topk_prob: bool = False,
                      router: str = "fixed_order") -> List[Dict[str, torch.Tensor]]:
     """Layer pass with tokens sharded over `len(xs)` ranks and experts owned per
-    `owner[e]`.  Mirrors dispatch -> local sorted-segment executor -> return ->
+    `owner[e]`, or per source rank `owner[s][e]` when experts are replicated
+    (the reference's dest_rank_table, utils/eval_core.py:672-717).  Mirrors dispatch -> local sorted-segment executor -> return ->
     unsort -> combine; the all-to-alls are list shuffles."""
     ep = len(xs)
     h = xs[0].shape[1]
@@ -279,7 +280,8 @@ def ep_block_forward(xs: List[torch.Tensor], cw: Dict[str, object], top_k: int,
             logits = router_logits_fixed_order(x, cw["router"], cw["router_bias"])
         topv, topi = softmax_topk(logits, top_k, norm_topk_prob, x.dtype)
         routed.append((logits, topv, topi))
-        plans.append(ep_dispatch_plan(topi, owner, ep))
+        own = torch.as_tensor(owner)
+        plans.append(ep_dispatch_plan(topi, own[len(plans)] if own.dim() == 2 else own, ep))
     # dispatch: chunk [src -> dst]
     send = []
     for r, x in enumerate(xs):

@@ -38,6 +38,9 @@ class MoeLayer(C.Structure):
 
 
 # name -> (restype, argtypes); this table is also what the symbol-export test walks.
+# rows up to which `sb_moe_layer_forward` takes the weight-streaming path (SB_DECODE_MAX_TOKENS)
+DECODE_MAX_TOKENS = 16
+
 SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_abi_version": (i32, []),
     "sb_last_error_string": (C.c_char_p, []),
@@ -52,6 +55,8 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_permute": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp, vp, vp, vp, vp, vp]),
     "sb_permute_noalloc": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
+    "sb_decode_experts": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32,
+                                vp, vp, vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
     "sb_peer_alloc": (i32, [sz, C.POINTER(vp)]),

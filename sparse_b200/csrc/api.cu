@@ -46,6 +46,7 @@ struct LayerScratch {
   char *permute_ws; size_t permute_ws_bytes;
   int32_t *tile_table, *expert_offsets, *slot_of_item, *item_of_slot;
   void *slot_scale, *shared_scale, *xs, *hbuf, *y, *shared_h, *shared_out;
+  float *router_ws;
   size_t total;
   int r_cap, t_cap;
 };
@@ -66,6 +67,7 @@ static LayerScratch carve(char *base, int T, int H, int E, int K, int I, int I_s
   s.item_of_slot = (int32_t *)take((size_t)s.r_cap * 4);
   s.slot_scale = take((size_t)s.r_cap * 2);
   s.shared_scale = take((size_t)s.t_cap * 2);
+  s.router_ws = (float *)take((size_t)SB_DECODE_MAX_TOKENS * (size_t)E * 4);
   s.xs = take((size_t)s.r_cap * H * 2);
   s.hbuf = take((size_t)s.r_cap * I * 2);
   s.y = take((size_t)s.r_cap * H * 2);
@@ -145,6 +147,17 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table, int32_t d
                                    R_cap, H, I, S, hbuf, out, status, static_cast<cudaStream_t>(stream));
 }
 
+int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
+                          const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
+                          const void *w2, const void *row_scale, int32_t H, int32_t I, int32_t n_slots,
+                          void *hbuf, void *y, const void *shared_w13, const void *shared_w2,
+                          const void *shared_scale, int32_t I_shared, int32_t T, void *shared_h,
+                          void *shared_out, int32_t *status, void *stream) {
+  return launch_decode_experts(x, item_of_slot, items_per_row, tile_table, slot_of_expert, w13, w2, row_scale,
+                               H, I, n_slots, hbuf, y, shared_w13, shared_w2, shared_scale, I_shared, T,
+                               shared_h, shared_out, status, static_cast<cudaStream_t>(stream));
+}
+
 int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
                    const void *shared_out, int32_t T, int32_t H, int32_t K, void *out, void *stream) {
   return launch_combine(rows_out, slot_of_item, idx, shared_out, T, H, K, out,
@@ -196,10 +209,26 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     return fail(SB_E_WORKSPACE, "sb_moe_layer_forward: workspace %zu < %zu bytes", L->ws_bytes, s.total);
 
   int32_t rc;
-  rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
-                     SB_DTYPE_BF16, L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits,
-                     L->shared_gate_w ? s.shared_scale : nullptr, stream);
+  if (T <= SB_DECODE_MAX_TOKENS)
+    rc = launch_router_decode(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
+                              L->router_fp32_logits, s.router_ws, L->topk_idx, L->topk_w, L->logits,
+                              L->shared_gate_w ? s.shared_scale : nullptr, s.expert_offsets, s.slot_of_item,
+                              s.item_of_slot, s.slot_scale, s.tile_table, stream);
+  else
+    rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
+                       SB_DTYPE_BF16, L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits,
+                       L->shared_gate_w ? s.shared_scale : nullptr, stream);
   if (rc != SB_OK) return rc;
+  if (T <= SB_DECODE_MAX_TOKENS) {
+    // decode-sized pass: the router launch already sorted the items (no gathered copy of x)
+    rc = launch_decode_experts(L->x, s.item_of_slot, K, s.tile_table, L->slot_of_expert, L->w13, L->w2,
+                               s.slot_scale, H, I, L->n_slots, s.hbuf, s.y, Is > 0 ? L->shared_w13 : nullptr,
+                               Is > 0 ? L->shared_w2 : nullptr, L->shared_gate_w ? s.shared_scale : nullptr,
+                               Is, T, s.shared_h, s.shared_out, status, stream);
+    if (rc != SB_OK) return rc;
+    return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
+                          L->out, stream);
+  }
   rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes,
                       s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
                       s.tile_table, stream);

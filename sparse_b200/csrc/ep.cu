@@ -85,60 +85,65 @@ __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epo
 }
 
 // One CTA.  Reads the complete counts matrix of this rank and writes
-//   dst_base[e]  first row, in owner(e)'s receive buffer, of THIS rank's items of expert e
+//   dst_base[e]  first row, in the destination's receive buffer, of THIS rank's items of expert e
 //   recv_offsets[E+1], tile table: this rank's receive-side expert segments
+// `owner` is the destination table [ep][E]: owner[s][e] = rank that executes
+// expert e for tokens on rank s (one row repeated for plain ownership, different
+// rows when hot experts are replicated and sources are spread over the replicas).
 __global__ void __launch_bounds__(256)
 ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict__ owner, int E,
                int rank, int ep, int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
                int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table) {
-  __shared__ int tot[kMaxExperts];        // items of expert e over all sources
-  __shared__ int before_me[kMaxExperts];  // items of expert e from sources < rank
-  __shared__ int seg_begin[kMaxExperts];  // first row of expert e in its owner's buffer
-  __shared__ int my_off[kMaxExperts + 1]; // receive-side offsets on this rank (0 for foreign experts)
-  __shared__ int tile_start[kMaxExperts + 1];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int t = 0, b = 0;
-    for (int s = 0; s < ep; ++s) {
-      int c = counts_all[(size_t)s * E + e];
-      if (s < rank) b += c;
-      t += c;
-    }
-    tot[e] = t; before_me[e] = b;
+  extern __shared__ int plan_smem[];
+  int *tot = plan_smem;                    // [ep][E] rows of expert e arriving at rank d
+  int *seg = tot + ep * E;                 // [ep][E] first row of expert e in rank d's buffer
+  int *my_off = seg + ep * E;              // [E+1]
+  int *tile_start = my_off + (E + 1);      // [E+1]
+  for (int i = threadIdx.x; i < ep * E; i += blockDim.x) {
+    const int d = i / E, e = i - d * E;
+    int t = 0;
+    for (int s = 0; s < ep; ++s)
+      if (owner[(size_t)s * E + e] == d) t += counts_all[(size_t)s * E + e];
+    tot[i] = t;
   }
   __syncthreads();
   if (threadIdx.x < ep) {
-    // per owner: running offset over its experts in ascending id
     const int d = threadIdx.x;
     int run = 0;
-    for (int e = 0; e < E; ++e)
-      if (owner[e] == d) { seg_begin[e] = run; run += tot[e]; }
+    for (int e = 0; e < E; ++e) { seg[d * E + e] = run; run += tot[d * E + e]; }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int ts = 0, last = 0;
+    int ts = 0;
     for (int e = 0; e < E; ++e) {
-      const bool mine = owner[e] == rank;
-      my_off[e] = mine ? seg_begin[e] : last;
+      my_off[e] = seg[rank * E + e];
       tile_start[e] = ts;
-      if (mine) { last = seg_begin[e] + tot[e]; ts += (tot[e] + tile_rows - 1) / tile_rows; }
+      ts += (tot[rank * E + e] + tile_rows - 1) / tile_rows;
     }
+    const int last = E > 0 ? seg[rank * E + E - 1] + tot[rank * E + E - 1] : 0;
     my_off[E] = last; tile_start[E] = ts;
     tile_table[0] = ts < tile_cap ? ts : tile_cap;
     tile_table[1] = last;
     tile_table[2] = tile_rows; tile_table[3] = 0;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) dst_base[e] = seg_begin[e] + before_me[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = owner[(size_t)rank * E + e];
+    int before = 0;
+    for (int s = 0; s < rank; ++s)
+      if (owner[(size_t)s * E + e] == d) before += counts_all[(size_t)s * E + e];
+    dst_base[e] = seg[d * E + e] + before;
+  }
   for (int e = threadIdx.x; e <= E; e += blockDim.x) recv_offsets[e] = my_off[e];
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    if (owner[e] != rank) continue;
+    const int n = tot[rank * E + e];
     const int nt = tile_start[e + 1] - tile_start[e];
     for (int m = 0; m < nt; ++m) {
       const int ti = tile_start[e] + m;
       if (ti >= tile_cap) break;
       int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
-      const int rb = seg_begin[e] + m * tile_rows;
-      const int re = min(seg_begin[e] + tot[e], rb + tile_rows);
+      const int rb = seg[rank * E + e] + m * tile_rows;
+      const int re = min(seg[rank * E + e] + n, rb + tile_rows);
       ent[0] = e; ent[1] = rb; ent[2] = re; ent[3] = 0;
     }
   }
@@ -305,7 +310,10 @@ int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, i
       rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
     return fail(SB_E_INVALID_ARG, "sb_ep_plan: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
   const int tile_cap = recv_cap / SB_TILE_M + E;
-  ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, owner, E, rank, ep, tile_cap,
+  const size_t smem = ((size_t)2 * ep * E + 2 * (size_t)(E + 1)) * sizeof(int);
+  if (smem > 48 * 1024)
+    SB_CUDA_CHECK(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  ep_plan_kernel<<<1, 256, smem, static_cast<cudaStream_t>(stream)>>>(counts_all, owner, E, rank, ep, tile_cap,
                                                                    sb_tile_rows(), dst_base, recv_offsets,
                                                                    tile_table);
   SB_LAUNCH_CHECK();

@@ -187,6 +187,7 @@ __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                 const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x16,
                  const int32_t *__restrict__ tile_table, int dense_rows,
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
@@ -242,13 +243,18 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
         const int tok0 = ch.tok_begin + (int)cta * (n >> 1);       // this CTA's half of the tokens
         const int wrow = wt * kTileW + (int)cta * kRowsPerCta;
+        // small groups fetch a small token box: a 3-token expert moves 2 KB of
+        // activations per K step, not 16 KB
+        const int half = n >> 1;
+        const CUtensorMap *tok_map = half <= 16 ? &tm_x16 : (half <= 64 ? &tm_x64 : &tm_x);
+        const uint32_t tok_bytes = (half <= 16 ? 16u : (half <= 64 ? 64u : 128u)) * kBlockK * 2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
           const uint32_t sa = smem_base + stage * kStageBytes;
-          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes);
+          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * (kABytes + tok_bytes));
           tma_pair_load_3d(sa, &tm_w, full_leader, kb * kBlockK, wrow, ch.slot);
-          tma_pair_load_2d(sa + kABytes, &tm_x, full_leader, kb * kBlockK, tok0);
+          tma_pair_load_2d(sa + kABytes, tok_map, full_leader, kb * kBlockK, tok0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -392,12 +398,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what) {
+int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what,
+                 uint32_t box_rows = kRowsPerCta) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(SB_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
-  cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)kRowsPerCta, 1};
+  cuuint32_t box[3] = {(cuuint32_t)kBlockK, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const cuuint32_t rank = d2 > 0 ? 3 : 2;
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(base), dims, strides, box,
@@ -409,12 +416,13 @@ int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, ui
 }
 
 template <int MODE>
-int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const int32_t *tile_table, int dense_rows,
+int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
                     int num_kb, int n_slots, int32_t *status, int grid, cudaStream_t stream) {
   auto kern = pair_gemm_kernel<MODE>;
   SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x, tile_table, dense_rows, slot_of_expert,
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
+                                              slot_of_expert,
                                               static_cast<const __nv_bfloat16 *>(row_scale),
                                               static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
                                               status);
@@ -439,11 +447,14 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (!rows || !w13 || !w2 || !hbuf || !out) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
   if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || !aligned(out, 16))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
-  CUtensorMap tm_x, tm_w13, tm_h, tm_w2;
+  CUtensorMap tm_x[3], tm_w13, tm_h[3], tm_w2;
+  const uint32_t boxes[3] = {128, 64, 16};
   int32_t rc;
-  if ((rc = make_map(&tm_x, rows, (uint64_t)H, (uint64_t)R_cap, 0, "rows")) != SB_OK) return rc;
+  for (int b = 0; b < 3; ++b) {
+    if ((rc = make_map(&tm_x[b], rows, (uint64_t)H, (uint64_t)R_cap, 0, "rows", boxes[b])) != SB_OK) return rc;
+    if ((rc = make_map(&tm_h[b], hbuf, (uint64_t)I, (uint64_t)R_cap, 0, "hbuf", boxes[b])) != SB_OK) return rc;
+  }
   if ((rc = make_map(&tm_w13, w13, (uint64_t)H, (uint64_t)2 * I, (uint64_t)S, "w13")) != SB_OK) return rc;
-  if ((rc = make_map(&tm_h, hbuf, (uint64_t)I, (uint64_t)R_cap, 0, "hbuf")) != SB_OK) return rc;
   if ((rc = make_map(&tm_w2, w2, (uint64_t)I, (uint64_t)H, (uint64_t)S, "w2")) != SB_OK) return rc;
   const int grid = (sb_device_sm_count() / 2) * 2;
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");

@@ -146,15 +146,16 @@ permute_fused_kernel(const int32_t *__restrict__ item_expert, const __nv_bfloat1
                      int32_t *__restrict__ slot_of_item, int32_t *__restrict__ item_of_slot,
                      __nv_bfloat16 *__restrict__ slot_scale, int32_t *__restrict__ tile_table) {
   extern __shared__ int fused_smem[];
-  int *hist = fused_smem;                    // [32][E] counts, then bases
-  int *offs = hist + 32 * E;                 // [E+1]
+  int *hist = fused_smem;                    // [nw][E] counts, then bases
+  const int nw = blockDim.x >> 5;            // warps in this CTA (1..32, fewer for few items)
+  int *offs = hist + nw * E;                 // [E+1]
   int *tile_start = offs + (E + 1);          // [E+1]
   int *tot = tile_start + (E + 1);           // [E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per_warp = ((n_items + 31) / 32 + 31) & ~31;     // items per warp, multiple of 32
+  const int per_warp = ((n_items + nw - 1) / nw + 31) & ~31;     // items per warp, multiple of 32
   const int begin = warp * per_warp;
   const int end = min(n_items, begin + per_warp);
-  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) hist[i] = 0;
+  for (int i = threadIdx.x; i < nw * E; i += blockDim.x) hist[i] = 0;
   __syncthreads();
   for (int i = begin + lane; i < end; i += 32) {
     const int e = item_expert[i];
@@ -163,7 +164,7 @@ permute_fused_kernel(const int32_t *__restrict__ item_expert, const __nv_bfloat1
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
-    for (int w = 0; w < 32; ++w) { const int c = hist[w * E + e]; hist[w * E + e] = run; run += c; }
+    for (int w = 0; w < nw; ++w) { const int c = hist[w * E + e]; hist[w * E + e] = run; run += c; }
     tot[e] = run;
   }
   __syncthreads();
@@ -276,11 +277,14 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
   int32_t *counts = static_cast<int32_t *>(ws);
   const int tile_cap = n_items / SB_TILE_M + E;
   if (n_items > 0 && n_items <= kFusedMaxItems) {
-    const size_t smem = ((size_t)32 * E + 2 * (size_t)(E + 1) + E) * sizeof(int);
+    // one warp per 512 items, at most 32: a decode step's handful of items is one warp's work
+    int nw = (n_items + 511) / 512;
+    nw = nw < 1 ? 1 : (nw > 32 ? 32 : nw);
+    const size_t smem = ((size_t)nw * E + 2 * (size_t)(E + 1) + E) * sizeof(int);
     if (smem > 48 * 1024)
       SB_CUDA_CHECK(cudaFuncSetAttribute(permute_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
-    permute_fused_kernel<<<1, 1024, smem, stream>>>(
+    permute_fused_kernel<<<1, nw * 32, smem, stream>>>(
         item_expert, static_cast<const __nv_bfloat16 *>(item_scale), n_items, E, tile_cap, sb_tile_rows(),
         expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale), tile_table);
     SB_LAUNCH_CHECK();

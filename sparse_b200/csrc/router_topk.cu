@@ -321,18 +321,80 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
   }
 }
 
-template <typename IN>
+template <typename LT, typename IN>
 __global__ void __launch_bounds__(kRouterThreads)
-softmax_topk_kernel(const IN *__restrict__ logits, int T, int E, int K, int renorm,
+softmax_topk_kernel(const LT *__restrict__ logits, int ld_logits, int T, int E, int K, int renorm,
                     int32_t *__restrict__ out_idx, IN *__restrict__ out_w) {
   __shared__ float slog[kRouterWarps][kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * kRouterWarps + warp;
   if (tok >= T) return;
-  for (int e = lane; e < E; e += 32) slog[warp][e] = Load8<IN>::load(logits + (size_t)tok * E + e);
+  for (int e = lane; e < E; e += 32) slog[warp][e] = Load8<LT>::load(logits + (size_t)tok * ld_logits + e);
   __syncwarp();
   warp_softmax_topk<IN>(slog[warp], E, K, renorm, lane, out_idx + (size_t)tok * K,
                         out_w + (size_t)tok * K);
+}
+
+// Decode-sized router: one warp per (token, router row), so a single token's 61
+// rows are streamed by 61 warps on 8 SMs instead of by one CTA.  Same per-lane
+// summation order as router_kernel (groups lane, lane+32, ...; even/odd partial
+// sums; butterfly), hence the same bits.  Logits go to `ws` as fp32 values
+// already rounded to the model dtype (unless fp32_logits); softmax_topk_kernel
+// finishes the job.
+template <typename IN>
+__global__ void __launch_bounds__(kRouterThreads)
+router_rows_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *__restrict__ bias,
+                   const IN *__restrict__ wsg, int T, int H, int E, int fp32_logits,
+                   float *__restrict__ ws, void *__restrict__ out_logits, IN *__restrict__ out_shared) {
+  constexpr int kVecPerGroup = sizeof(IN) == 2 ? 1 : 2;
+  const int NR = E + (wsg != nullptr ? 1 : 0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x;
+  const int row = blockIdx.y * kRouterWarps + warp;
+  if (row >= NR) return;
+  const IN *wrow = (row < E) ? wg + (size_t)row * H : wsg;
+  const IN *xrow = x + (size_t)tok * H;
+  const int G = H / 8;
+  Acc2 acc = Acc2::zero();
+  for (int g0 = 0; g0 < G; g0 += 32 * 4) {
+    uint4 wq[4][kVecPerGroup], xq[4][kVecPerGroup];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int v = 0; v < kVecPerGroup; ++v) {
+        const int g = g0 + u * 32 + lane;
+        wq[u][v] = make_uint4(0, 0, 0, 0); xq[u][v] = make_uint4(0, 0, 0, 0);
+        if (g < G) {
+          wq[u][v] = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)g * 8) + v);
+          xq[u][v] = __ldg(reinterpret_cast<const uint4 *>(xrow + (size_t)g * 8) + v);
+        }
+      }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (g0 + u * 32 + lane < G) {
+        Pair4<IN> wv, xv;
+        wv.load(&wq[u][0]);
+        xv.load(&xq[u][0]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc.fma(xv, wv, i);
+      }
+    }
+  }
+  float sum = butterfly_sum(acc.lane_sum());
+  if (lane == 0) {
+    if (row < E) {
+      if (bias != nullptr) sum = __fadd_rn(sum, bias[row]);
+      const float lg = fp32_logits ? sum : Load8<IN>::round_model(sum);
+      ws[(size_t)tok * E + row] = lg;
+      if (out_logits != nullptr) {
+        if (fp32_logits) static_cast<float *>(out_logits)[(size_t)tok * E + row] = lg;
+        else Load8<IN>::store(static_cast<IN *>(out_logits) + (size_t)tok * E + row, lg);
+      }
+    } else {
+      const float v = Load8<IN>::round_model(sum);
+      Load8<IN>::store(out_shared + tok, __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v))));
+    }
+  }
 }
 
 template <typename IN, int TB>
@@ -400,6 +462,111 @@ int32_t launch_router(const void *x, const void *wg, const float *bias, const vo
   return fail(SB_E_INVALID_ARG, "sb_router_topk: unknown dtype %d", dtype);
 }
 
+namespace {
+
+// Decode-sized softmax/top-k AND expert sort in one CTA: warp t finishes token
+// t (same arithmetic as softmax_topk_kernel), then the T*K items (at most 128)
+// are ranked by (expert id, item index) with an all-pairs count, which yields
+// the same stable expert-sorted order, offsets and tile table as the permute
+// kernels.
+constexpr int kSmallMaxItems = 16 * kMaxK;
+
+__global__ void __launch_bounds__(512)
+route_sort_small_kernel(const float *__restrict__ logits, int T, int E, int K, int renorm, int tile_rows,
+                        int tile_cap, int32_t *__restrict__ out_idx, __nv_bfloat16 *__restrict__ out_w,
+                        int32_t *__restrict__ expert_offsets, int32_t *__restrict__ slot_of_item,
+                        int32_t *__restrict__ item_of_slot, __nv_bfloat16 *__restrict__ slot_scale,
+                        int32_t *__restrict__ tile_table) {
+  __shared__ float slog[16][kMaxExperts];
+  __shared__ int s_exp[kSmallMaxItems];
+  __shared__ int s_off[kMaxExperts + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < T) {
+    for (int e = lane; e < E; e += 32) slog[warp][e] = logits[(size_t)warp * E + e];
+    __syncwarp();
+    warp_softmax_topk<__nv_bfloat16>(slog[warp], E, K, renorm, lane, out_idx + (size_t)warp * K,
+                                     out_w + (size_t)warp * K);
+  }
+  __syncthreads();                       // this CTA's global writes are visible to all its threads
+  const int n = T * K;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = out_idx[i];
+    s_exp[i] = (e >= 0 && e < E) ? e : -1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    int below = 0;
+    for (int j = 0; j < n; ++j) below += (s_exp[j] >= 0 && s_exp[j] < e) ? 1 : 0;
+    s_off[e] = below;
+    expert_offsets[e] = below;
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = s_exp[i];
+    int slot = -1;
+    if (e >= 0) {
+      slot = 0;
+      for (int j = 0; j < n; ++j) slot += (s_exp[j] >= 0 && (s_exp[j] < e || (s_exp[j] == e && j < i))) ? 1 : 0;
+      item_of_slot[slot] = i;
+      slot_scale[slot] = out_w[i];
+    }
+    slot_of_item[i] = slot;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int ts = 0;                          // tiles of the experts below e
+    for (int j = 0; j < e; ++j) ts += (s_off[j + 1] - s_off[j] + tile_rows - 1) / tile_rows;
+    const int cnt = s_off[e + 1] - s_off[e];
+    const int nt = (cnt + tile_rows - 1) / tile_rows;
+    for (int m = 0; m < nt; ++m) {
+      const int ti = ts + m;
+      if (ti >= tile_cap) break;
+      int32_t *ent = tile_table + kTileHeaderInts + (size_t)ti * kTileEntryInts;
+      const int rb = s_off[e] + m * tile_rows;
+      ent[0] = e; ent[1] = rb; ent[2] = min(s_off[e + 1], rb + tile_rows); ent[3] = 0;
+    }
+    if (e == E - 1) {
+      const int all = ts + nt;
+      tile_table[0] = all < tile_cap ? all : tile_cap;
+      tile_table[1] = s_off[E];
+      tile_table[2] = tile_rows; tile_table[3] = 0;
+    }
+  }
+}
+
+}  // namespace
+
+int32_t launch_router_decode(const void *x, const void *wg, const float *bias, const void *wsg, int T, int H,
+                             int E, int K, int renorm, int fp32_logits, float *ws, int32_t *out_idx,
+                             void *out_w, void *out_logits, void *out_shared_scale, int32_t *expert_offsets,
+                             int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale, int32_t *tile_table,
+                             cudaStream_t stream) {
+  if (T <= 0) return SB_OK;
+  if (H % 8 != 0 || E < 1 || E > kMaxExperts || K < 1 || K > kMaxK || K > E || !ws)
+    return fail(SB_E_INVALID_ARG, "router (decode): bad arguments");
+  const int NR = E + (wsg ? 1 : 0);
+  dim3 grid(T, (NR + kRouterWarps - 1) / kRouterWarps);
+  router_rows_kernel<__nv_bfloat16><<<grid, kRouterThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(wg), bias,
+      static_cast<const __nv_bfloat16 *>(wsg), T, H, E, fp32_logits, ws, out_logits,
+      static_cast<__nv_bfloat16 *>(out_shared_scale));
+  SB_LAUNCH_CHECK();
+  if (tile_table != nullptr) {
+    // softmax/top-k and the expert sort in one single-CTA launch
+    if (T > 16 || !expert_offsets || !slot_of_item || !item_of_slot || !slot_scale)
+      return fail(SB_E_INVALID_ARG, "router (decode): sort outputs need T <= 16 and all tables");
+    const int warps = T > 4 ? 16 : 4;
+    route_sort_small_kernel<<<1, warps * 32, 0, stream>>>(
+        ws, T, E, K, renorm, sb_tile_rows(), T * K / SB_TILE_M + E, out_idx, static_cast<__nv_bfloat16 *>(out_w),
+        expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale), tile_table);
+    SB_LAUNCH_CHECK();
+    return SB_OK;
+  }
+  softmax_topk_kernel<float, __nv_bfloat16><<<(T + kRouterWarps - 1) / kRouterWarps, kRouterThreads, 0, stream>>>(
+      ws, E, T, E, K, renorm, out_idx, static_cast<__nv_bfloat16 *>(out_w));
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
 int32_t launch_softmax_topk(const void *logits, int T, int E, int K, int renorm, int dtype,
                             int32_t *out_idx, void *out_w, cudaStream_t stream) {
   if (T < 0 || E < 1 || E > kMaxExperts || K < 1 || K > kMaxK || K > E)
@@ -408,12 +575,12 @@ int32_t launch_softmax_topk(const void *logits, int T, int E, int K, int renorm,
   if (!logits || !out_idx || !out_w) return fail(SB_E_INVALID_ARG, "sb_softmax_topk: null pointer");
   int blocks = (T + kRouterWarps - 1) / kRouterWarps;
   if (dtype == SB_DTYPE_BF16)
-    softmax_topk_kernel<__nv_bfloat16><<<blocks, kRouterThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(logits), T, E, K, renorm, out_idx,
+    softmax_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, kRouterThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(logits), E, T, E, K, renorm, out_idx,
         static_cast<__nv_bfloat16 *>(out_w));
   else if (dtype == SB_DTYPE_F32)
-    softmax_topk_kernel<float><<<blocks, kRouterThreads, 0, stream>>>(
-        static_cast<const float *>(logits), T, E, K, renorm, out_idx, static_cast<float *>(out_w));
+    softmax_topk_kernel<float, float><<<blocks, kRouterThreads, 0, stream>>>(
+        static_cast<const float *>(logits), E, T, E, K, renorm, out_idx, static_cast<float *>(out_w));
   else
     return fail(SB_E_INVALID_ARG, "sb_softmax_topk: unknown dtype %d", dtype);
   SB_LAUNCH_CHECK();

@@ -64,6 +64,11 @@ int32_t launch_router(const void *x, const void *wg, const float *bias, const vo
                       int T, int H, int E, int K, int renorm, int dtype, int fp32_logits,
                       int32_t *out_idx, void *out_w, void *out_logits, void *out_shared_scale,
                       cudaStream_t stream);
+int32_t launch_router_decode(const void *x, const void *wg, const float *bias, const void *wsg, int T, int H,
+                             int E, int K, int renorm, int fp32_logits, float *ws, int32_t *out_idx,
+                             void *out_w, void *out_logits, void *out_shared_scale, int32_t *expert_offsets,
+                             int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale, int32_t *tile_table,
+                             cudaStream_t stream);
 int32_t launch_softmax_topk(const void *logits, int T, int E, int K, int renorm, int dtype,
                             int32_t *out_idx, void *out_w, cudaStream_t stream);
 int32_t launch_permute(const void *x, const int32_t *item_expert, const void *item_scale,
@@ -79,6 +84,12 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
                                    const void *w13, const void *w2, const int32_t *slot_of_expert,
                                    const void *row_scale, int R_cap, int H, int I, int S,
                                    void *hbuf, void *out, int32_t *status, cudaStream_t stream);
+int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int items_per_row,
+                              const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
+                              const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
+                              void *y, const void *shared_w13, const void *shared_w2,
+                              const void *shared_scale, int I_sh, int T, void *shared_h, void *shared_out,
+                              int32_t *status, cudaStream_t stream);
 int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
                        const void *shared_out, int T, int H, int K, void *out,
                        cudaStream_t stream);

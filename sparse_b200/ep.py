@@ -44,33 +44,42 @@ def recv_capacity(max_tokens: int, top_k: int, ep: int) -> int:
     return _round_up(max(1, max_tokens * top_k * ep), _TILE)
 
 
+def owner_table(owner, ep: int, num_experts: int) -> torch.Tensor:
+    """Destination table int32 [ep][E] from either one ownership row [E] or a
+    per-source table [ep][E] (e.g. `Placement.dest_table`)."""
+    t = torch.as_tensor(owner, dtype=torch.int32)
+    if t.dim() == 1:
+        t = t.unsqueeze(0).expand(ep, -1)
+    if tuple(t.shape) != (ep, num_experts):
+        raise ValueError("owner table must be [E] or [ep,E] = [%d,%d], got %s" % (ep, num_experts, tuple(t.shape)))
+    if int(t.min()) < 0 or int(t.max()) >= ep:
+        raise ValueError("owner table holds a rank outside [0,%d)" % ep)
+    return t.contiguous()
+
+
 def plan_layout_reference(counts_all: torch.Tensor, owner: torch.Tensor, rank: int):
     """Host mirror of `sb_ep_plan` (integer arithmetic on CPU tensors), used by the
-    debug checks and the CPU tests.  counts_all int [ep,E], owner int [E].
-    Returns (dst_base [E], recv_offsets [E+1], seg_begin [E]): rows of expert e
-    coming from source s sit at seg_begin[e] + sum(counts_all[:s, e]) in the
-    owner's receive buffer; the buffer is ordered by expert id, then source rank,
-    then the source's stable item order."""
+    debug checks and the CPU tests.  counts_all int [ep,E]; owner int [E] or
+    [ep,E] (owner[s][e] = destination of expert e for source s).
+    Returns (dst_base [E], recv_offsets [E+1], seg_begin [ep,E]): rows of expert e
+    coming from source s sit, in rank d = owner[s][e]'s receive buffer, at
+    seg_begin[d][e] + (rows of e from sources s' < s that also go to d); a buffer
+    is ordered by expert id, then source rank, then the source's stable item order."""
     counts_all = counts_all.to(torch.long)
-    owner = owner.to(torch.long)
     ep, e = counts_all.shape
-    tot = counts_all.sum(0)
-    seg_begin = torch.zeros(e, dtype=torch.long)
-    for d in range(ep):
-        mine = (owner == d).nonzero().flatten()
-        run = torch.cumsum(tot[mine], 0) - tot[mine]
-        seg_begin[mine] = run
-    before = counts_all[:rank].sum(0)
-    dst_base = seg_begin + before
+    own = owner_table(owner, ep, e).to(torch.long)
+    tot = torch.zeros((ep, e), dtype=torch.long)
+    for s in range(ep):
+        tot[own[s], torch.arange(e)] += counts_all[s]
+    seg_begin = torch.cumsum(tot, 1) - tot
+    dst = own[rank]
+    before = torch.zeros(e, dtype=torch.long)
+    for s in range(rank):
+        before += torch.where(own[s] == dst, counts_all[s], torch.zeros_like(counts_all[s]))
+    dst_base = seg_begin[dst, torch.arange(e)] + before
     recv_offsets = torch.zeros(e + 1, dtype=torch.long)
-    last = 0
-    for ex in range(e):
-        if int(owner[ex]) == rank:
-            recv_offsets[ex] = seg_begin[ex]
-            last = int(seg_begin[ex] + tot[ex])
-        else:
-            recv_offsets[ex] = last
-    recv_offsets[e] = last
+    recv_offsets[:e] = seg_begin[rank]
+    recv_offsets[e] = int(tot[rank].sum())
     return dst_base, recv_offsets, seg_begin
 
 
@@ -162,7 +171,8 @@ class EpRank:
         self.max_tokens = max_tokens
         n = max_tokens * top_k
         i32, bf = torch.int32, torch.bfloat16
-        self.owner = torch.tensor(list(owner), dtype=i32, device=dev)
+        self.owner = owner_table(owner, ep, e).to(dev)              # [ep][E]
+        self.owner_row = self.owner[rank]                            # this rank's destinations
         self.topk_idx = torch.empty((max_tokens, top_k), dtype=i32, device=dev)
         self.topk_w = torch.empty((max_tokens, top_k), dtype=bf, device=dev)
         self.logits = torch.empty((max_tokens, e), dtype=torch.float32 if fp32_logits else bf, device=dev)
@@ -236,7 +246,7 @@ class EpRank:
         check(lib.sb_ep_dispatch(
             self._x.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(),
             self.slot_of_item.data_ptr(), self.local_offsets.data_ptr(), self.dst_base.data_ptr(),
-            self.owner.data_ptr(), t * k, k, w.hidden, self.ep, self.bufs.recv_cap,
+            self.owner_row.data_ptr(), t * k, k, w.hidden, self.ep, self.bufs.recv_cap,
             self.bufs.ptr_array("rows"), self.bufs.ptr_array("scale"), self.item_rank.data_ptr(),
             self.item_row.data_ptr(), self._s()), "sb_ep_dispatch")
         self.launches += 1

@@ -148,7 +148,7 @@ class DistributedSparseMoeBlock(nn.Module):
                 from .ep import ExpertParallelLayer
                 table = self.placement.dest_table(self.layer_idx, "prefill")
                 self._ep = ExpertParallelLayer(lw, top_k, max_tokens, self.comm_rank, self.comm_world,
-                                               process_group, owner=table[self.comm_rank],
+                                               process_group, owner=table,
                                                renorm=self.norm_topk_prob, fp32_logits=fp32_logits)
             else:
                 self._runner = LayerRunner(lw, top_k, max_tokens, renorm=self.norm_topk_prob,

@@ -22,6 +22,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Set, Tuple
 import torch
 
 from . import _lib, ops
+from ._lib import DECODE_MAX_TOKENS
 from .cache import ExpertWeightCache, SlotPool
 from .config import BlockConfig
 from .context import Metrics, SparseContext
@@ -408,12 +409,35 @@ class CachedLayerRunner:
         hbuf = torch.empty((p.r_cap, w.inter), dtype=torch.bfloat16, device=w.device)
         y = torch.empty((p.r_cap, w.hidden), dtype=torch.bfloat16, device=w.device)
 
+        # Up to DECODE_MAX_TOKENS rows take the same weight-streaming kernels the
+        # resident layer uses at that size, so both stay bit-identical; the
+        # shared expert rides in the first of those launches.
+        decode = t <= DECODE_MAX_TOKENS
+        shared_h = shared_dec = None
+        if decode and w.shared_inter:
+            shared_h = torch.empty((t, w.shared_inter), dtype=torch.bfloat16, device=w.device)
+            shared_dec = torch.empty((t, w.hidden), dtype=torch.bfloat16, device=w.device)
+        shared_pending = [decode and bool(w.shared_inter)]
+
         def gemm():
+            stream = torch.cuda.current_stream(w.device).cuda_stream
+            if decode:
+                with_shared = shared_pending[0]
+                shared_pending[0] = False
+                _lib.check(_lib.lib.sb_decode_experts(
+                    x.data_ptr(), p.item_of_slot.data_ptr(), k, p.tile_table.data_ptr(),
+                    w.slot_of_expert.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(), p.slot_scale.data_ptr(),
+                    w.hidden, w.inter, w.n_slots, hbuf.data_ptr(), y.data_ptr(),
+                    w.shared_w13.data_ptr() if with_shared else 0, w.shared_w2.data_ptr() if with_shared else 0,
+                    shared_scale.data_ptr() if with_shared and shared_scale is not None else 0,
+                    w.shared_inter if with_shared else 0, t,
+                    shared_h.data_ptr() if with_shared else 0, shared_dec.data_ptr() if with_shared else 0,
+                    self.status.data_ptr(), stream), "sb_decode_experts")
+                return
             _lib.check(_lib.lib.sb_grouped_swiglu(
                 p.rows.data_ptr(), p.tile_table.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
                 w.slot_of_expert.data_ptr(), p.slot_scale.data_ptr(), p.r_cap, w.hidden, w.inter, w.n_slots,
-                hbuf.data_ptr(), y.data_ptr(), self.status.data_ptr(),
-                torch.cuda.current_stream(w.device).cuda_stream), "sb_grouped_swiglu")
+                hbuf.data_ptr(), y.data_ptr(), self.status.data_ptr(), stream), "sb_grouped_swiglu")
 
         protect = set(needed)
         self.launch_groups = 0
@@ -463,7 +487,11 @@ class CachedLayerRunner:
                 run_group([plan.residual] + plan.rest)    # a hit that waits for the prefetch event
         st.note_compute_done()
         shared_out = None
-        if w.shared_inter:
+        if decode and w.shared_inter:
+            if shared_pending[0]:                         # no routed launch happened (cannot occur with top_k >= 1)
+                gemm()
+            shared_out = shared_dec
+        elif w.shared_inter:
             shared_out, _ = ops.grouped_swiglu(x, w.shared_w13, w.shared_w2, dense_rows=t, row_scale=shared_scale,
                                                status=self.status)
         out = ops.combine(y, p.slot_of_item, idx, shared_out, t)

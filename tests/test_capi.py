@@ -59,3 +59,11 @@ def test_bad_arguments_are_rejected_with_a_message():
 def test_struct_layout_matches_header():
     from sparse_b200._lib import MoeLayer, lib
     assert C.sizeof(MoeLayer) == lib.sb_moe_layer_struct_bytes()
+
+
+def test_decode_limit_matches_header():
+    import re
+    from sparse_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "sparse_b200.h")).read()
+    m = re.search(r"#define\s+SB_DECODE_MAX_TOKENS\s+(\d+)", text)
+    assert m and int(m.group(1)) == _lib.DECODE_MAX_TOKENS

@@ -43,6 +43,7 @@ def _worker(rank, world, init_file, result_file):
         dist.all_gather(gathered, counts)
         counts_all = torch.stack(gathered)
         dst_base, recv_offsets, seg_begin = plan_layout_reference(counts_all, owner, rank)
+        assert seg_begin.shape == (world, e)
         # where every local item goes
         item_row = dst_base[flat] + (slot_of_item - local_off[flat])
         item_rank = owner[flat]
@@ -104,7 +105,7 @@ def test_plan_reference_small_known_answer():
     owner = torch.tensor([0, 1, 0, 1])
     d0, r0, s0 = plan_layout_reference(counts, owner, 0)
     d1, r1, s1 = plan_layout_reference(counts, owner, 1)
-    assert s0.tolist() == [0, 0, 3, 4]
+    assert s0[0].tolist() == [0, 3, 3, 4] and s0[1].tolist() == [0, 0, 4, 4]
     assert d0.tolist() == [0, 0, 3, 4]
     assert d1.tolist() == [2, 0, 4, 7]
     assert r0.tolist() == [0, 3, 3, 4, 4]

@@ -112,3 +112,72 @@ def test_real_ranks_over_peer_memory(world):
     sys.stderr.write(res.stderr[-3000:])
     assert res.returncode == 0
     assert res.stdout.count("EP_WORKER_OK") == world
+
+
+def test_simulated_ranks_with_replicated_placement():
+    """A hot expert replicated on several ranks, every source rank sending to its
+    own replica (per-source destination table): rows still equal the single-GPU
+    layer bit for bit, and the load is spread."""
+    from sparse_b200.ep import EpRank, PeerBuffers, recv_capacity
+    from sparse_b200.layer import LayerRunner, LayerWeights
+    from sparse_b200.placement import Placement, balanced_replicated_placement
+    dev = torch.device("cuda:0")
+    shape = synth.TINY
+    w = block_weights("TINY", 1.2)
+    ep, tokens = 4, [64, 64, 64, 64]
+    x_all = synth.make_hidden(sum(tokens), shape.hidden, seed=5).to(torch.bfloat16)
+    res = mo.moe_block_forward(x_all, mo.cast_weights(w, torch.bfloat16), shape.top_k)
+    load = torch.bincount(res["topi"].reshape(-1), minlength=shape.num_experts).tolist()
+    obj = balanced_replicated_placement([load], ep)
+    plc = Placement("scp_ep", 1, shape.num_experts, ep, obj=obj, apply_decode=True)
+    table = plc.dest_table(0, "prefill")
+    assert len({tuple(r) for r in table}) > 1, "sources must use different replicas of the hot expert"
+    cap = recv_capacity(max(tokens), shape.top_k, ep)
+    bufs = [PeerBuffers(shape.hidden, shape.num_experts, cap, ep, r) for r in range(ep)]
+    for b in bufs:
+        b.allocate_local()
+    for b in bufs:
+        for p in range(ep):
+            b.adopt_local_peer(p, bufs[p])
+    ranks = []
+    for r in range(ep):
+        held = sorted(plc.receive_experts(0, r, "prefill"))
+        from sparse_b200.layer import LayerWeights as LW
+        lw = LW(shape.hidden, shape.inter, shape.num_experts, max(1, len(held)), shape.shared_inter, dev)
+        lw.set_router(w.router, w.router_bias)
+        slot_of = [-1] * shape.num_experts
+        for s, e in enumerate(held):
+            lw.load_expert(s, w.gate[e], w.up[e], w.down[e])
+            slot_of[e] = s
+        lw.set_slot_map(slot_of)
+        lw.set_shared(w.sh_gate, w.sh_up, w.sh_down, w.sh_scalar_gate)
+        ranks.append(EpRank(lw, shape.top_k, max(tokens), r, ep, table, bufs[r]))
+    xs = [t.contiguous().to(dev) for t in torch.split(x_all, tokens)]
+    try:
+        for r in range(ep):
+            ranks[r].stage_route(xs[r])
+        for r in range(ep):
+            ranks[r].stage_publish()
+        torch.cuda.synchronize()
+        for r in range(ep):
+            ranks[r].stage_plan(); ranks[r].stage_dispatch(); ranks[r].stage_shared()
+        torch.cuda.synchronize()
+        for r in range(ep):
+            ranks[r].stage_experts()
+        torch.cuda.synchronize()
+        got = torch.cat([ranks[r].stage_combine().clone() for r in range(ep)])
+        torch.cuda.synchronize()
+        for r in range(ep):
+            assert int(ranks[r].status.item()) == 0
+        runner = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, sum(tokens))
+        ref_out, _, _, _ = runner.forward(x_all.to(dev))
+        assert torch.equal(got, ref_out)
+        recv = [int(ranks[r].recv_offsets[-1].item()) for r in range(ep)]
+        assert sum(recv) == sum(tokens) * shape.top_k
+        assert max(recv) < 0.45 * sum(recv), recv
+        sim = mo.ep_block_forward([x.cpu() for x in xs], mo.cast_weights(w, torch.bfloat16), shape.top_k,
+                                  torch.tensor(table))
+        assert [int(s["recv_i"].numel()) for s in sim] == recv
+    finally:
+        for b in bufs:
+            b.close()

@@ -294,8 +294,10 @@ def _run_layer(shape_name, tokens, zipf, seed, fp32_logits=False):
 
 
 @pytest.mark.parametrize("shape_name,tokens,zipf", [
-    ("TINY", 1, 0.0), ("TINY", 3, 0.0), ("TINY", 17, 0.0), ("TINY", 130, 1.2), ("TINY", 1000, 1.2),
-    ("QWEN_MOE", 1, 1.2), ("QWEN_MOE", 8, 1.2), ("QWEN_MOE", 64, 1.2), ("QWEN_MOE", 256, 1.2),
+    ("TINY", 1, 0.0), ("TINY", 3, 0.0), ("TINY", 9, 1.2), ("TINY", 16, 0.0), ("TINY", 17, 0.0),
+    ("TINY", 130, 1.2), ("TINY", 1000, 1.2),
+    ("QWEN_MOE", 1, 1.2), ("QWEN_MOE", 8, 1.2), ("QWEN_MOE", 13, 1.2), ("QWEN_MOE", 16, 0.0),
+    ("QWEN_MOE", 64, 1.2), ("QWEN_MOE", 256, 1.2),
     ("QWEN_MOE", 512, 0.0),
 ])
 def test_layer_against_oracle(shape_name, tokens, zipf):
@@ -307,7 +309,7 @@ def test_layer_against_oracle(shape_name, tokens, zipf):
     assert int(_bf16_ulp_diff(wts, res["topv"]).max()) <= 1
     assert rel_l2(out, res["out"]) < REL_L2
     assert float((out.float() - res["out"].float()).abs().max()) < MAX_ABS
-    assert runner.last_launches >= 8
+    assert runner.last_launches >= 5
 
 
 @pytest.mark.parametrize("name", ["qwen_bf16_zipf_t1", "qwen_bf16_zipf_t64", "qwen_bf16_zipf_t256",
