@@ -163,7 +163,7 @@ def run_reference_arm(args):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ------------------------------------------------------------------ GPU arm ----
@@ -298,8 +298,28 @@ def run_ours(args):
     shape = synth.QWEN_MOE
     t = TOKENS_PER_GPU
     w = synth.make_weights(shape, weight_seed=0, zipf_s=ZIPF_S)
+    placement = None
+    placement_note = "single GPU"
+    if world > 1 and args.placement == "balanced":
+        # Profile -> placement, as the reference's offline solver does for its
+        # replicated placements: expert load of a seeded calibration batch
+        # (not a bench input), hot experts replicated, sources spread over replicas.
+        from sparse_b200 import ops
+        from sparse_b200.placement import Placement, balanced_replicated_placement
+        xc = synth.make_hidden(4096, shape.hidden, seed=424242).to(torch.bfloat16).to(dev)
+        idx_c, _, _, _ = ops.router_topk(xc, w.router.to(torch.bfloat16).to(dev), shape.top_k,
+                                         bias=None if w.router_bias is None else w.router_bias.float().to(dev))
+        load = torch.bincount(idx_c.reshape(-1).long().cpu(), minlength=shape.num_experts).tolist()
+        obj = balanced_replicated_placement([load], world)
+        placement = Placement("scp_ep", 1, shape.num_experts, world, obj=obj, apply_decode=True)
+        held = [len(placement.receive_experts(0, r, "prefill")) for r in range(world)]
+        placement_note = ("load-balanced replicated placement from a calibration batch's expert histogram; "
+                          "experts held per rank %s" % held)
+    elif world > 1:
+        placement_note = "round-robin ownership (e %% %d)" % world
     block = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=t,
-                                            process_group=None if world == 1 else dist.group.WORLD)
+                                            process_group=None if world == 1 else dist.group.WORLD,
+                                            placement=placement)
     xs_host = [synth.make_hidden(t, shape.hidden, seed=1 + 97 * rank + b).to(torch.bfloat16).pin_memory()
                for b in range(N_INPUT_BATCHES)]
     xs = [xh.to(dev) for xh in xs_host]
@@ -362,6 +382,7 @@ def run_ours(args):
                    "top_k": shape.top_k, "hidden": shape.hidden, "inter": shape.inter,
                    "shared_inter": shape.shared_inter,
                    "parallelism": "ep%d" % world if world > 1 else "ep1",
+                   "placement": placement_note,
                    "l2": "weights 1.1 GB per layer exceed the 126 MB L2; %d input batches rotated" % N_INPUT_BATCHES},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": t * shape.hidden * 2 * world,
                 "d2h_bytes_per_step": t * shape.hidden * 2 * world},
@@ -440,13 +461,32 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": "first %d of the %d tokens, fp32, 3 steps after 1 warm-up" % (
                                         CPU_SAMPLE_TOKENS, t)}
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """The one JSON line, on the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; the
+    # contract is one JSON line there.  Everything else goes to stderr.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -454,6 +494,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode-to-prefill token sweep")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "rr"],
+                    help="expert placement at N>1: load-balanced replicated (default) or round-robin")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

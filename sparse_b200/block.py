@@ -25,7 +25,7 @@ class B200MoeBlock:
     def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int,
                  norm_topk_prob: bool = False, fp32_router_logits: bool = False,
                  return_router_logits: bool = True, ep_rank: int = 0, ep_size: int = 1,
-                 process_group=None):
+                 process_group=None, owner=None):
         self.weights = weights
         self.device = weights.device
         self.top_k = top_k
@@ -37,22 +37,30 @@ class B200MoeBlock:
         if ep_size > 1:
             from .ep import ExpertParallelLayer
             self._ep = ExpertParallelLayer(weights, top_k, max_tokens, ep_rank, ep_size,
-                                           process_group, renorm=norm_topk_prob,
+                                           process_group, owner=owner, renorm=norm_topk_prob,
                                            fp32_logits=fp32_router_logits)
         self._x_stage: Optional[torch.Tensor] = None
         self.last_launches = 0
 
     @classmethod
     def from_block_weights(cls, w, device: torch.device, ep_rank: int = 0, ep_size: int = 1,
-                           max_tokens: int = 4096, process_group=None) -> "B200MoeBlock":
+                           max_tokens: int = 4096, process_group=None, placement=None,
+                           layer_idx: int = 0, stage: str = "prefill") -> "B200MoeBlock":
         """Build from seeded `synth.BlockWeights`; at ep_size > 1 only the
-        experts owned by `ep_rank` (round-robin, e % ep_size) are loaded."""
+        experts this rank serves are loaded: round-robin (e % ep_size) by default,
+        or every expert a `placement.Placement` lists `ep_rank` as a replica of,
+        with that placement's per-source destination table."""
         s = w.shape
+        owner = None
         if ep_size == 1:
             lw = LayerWeights.from_block_weights(w, device)
         else:
-            owned = [e for e in range(s.num_experts) if e % ep_size == ep_rank]
-            lw = LayerWeights(s.hidden, s.inter, s.num_experts, len(owned), s.shared_inter, device)
+            if placement is not None:
+                owned = sorted(placement.receive_experts(layer_idx, ep_rank, stage))
+                owner = placement.dest_table(layer_idx, stage)
+            else:
+                owned = [e for e in range(s.num_experts) if e % ep_size == ep_rank]
+            lw = LayerWeights(s.hidden, s.inter, s.num_experts, max(1, len(owned)), s.shared_inter, device)
             lw.set_router(w.router, w.router_bias)
             slot_of = [-1] * s.num_experts
             for slot, e in enumerate(owned):
@@ -63,7 +71,7 @@ class B200MoeBlock:
                 lw.set_shared(w.sh_gate, w.sh_up, w.sh_down, w.sh_scalar_gate)
         return cls(lw, s.top_k, max_tokens, norm_topk_prob=s.norm_topk_prob,
                    fp32_router_logits=not s.shared_gate and s.num_experts == 64,
-                   ep_rank=ep_rank, ep_size=ep_size, process_group=process_group)
+                   ep_rank=ep_rank, ep_size=ep_size, process_group=process_group, owner=owner)
 
     # -- the three entry points -----------------------------------------------------
     def forward_device(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

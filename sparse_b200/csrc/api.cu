@@ -5,6 +5,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "sb_common.cuh"
 
 namespace sb {
@@ -30,15 +32,74 @@ void reset_launch_count() { g_launches = 0; }
 
 static inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Side stream and fork/join events for the light-group kernels, one set per
+// device, created on first use.  Holding the mutex over a fork..join enqueue
+// keeps two host threads from interleaving their records on the shared events.
+struct SideLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static std::mutex g_side_mu;
+static SideLane g_side[64];
+
+static SideLane *side_lane() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SideLane &l = g_side[dev];
+  if (l.stream == nullptr) {
+    if (cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) != cudaSuccess) { l.stream = nullptr; return nullptr; }
+    if (cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaStreamDestroy(l.stream);
+      l.stream = nullptr;
+      return nullptr;
+    }
+  }
+  return &l;
+}
+
+static int hybrid_rows() {
+  static const int v = [] {
+    const char *e = getenv("SPARSE_B200_HYBRID");
+    return (e && strcmp(e, "1") == 0) ? SB_DECODE_MAX_TOKENS : 0;
+  }();
+  return v;
+}
+
+// The grouped expert MLP.  Experimental split, off unless SPARSE_B200_HYBRID=1:
+// with the CTA-pair kernel and a tile table, groups of at most 16 rows go to
+// the weight-streaming kernels on a side stream while the tensor-core kernel
+// works on the rest.  Measured on B200 it loses to the tile kernel alone (one
+// streaming CTA per SM beside a GEMM CTA moves 1.7 TB/s; the tile kernel
+// already hides most light tiles behind heavy ones), so it is not the default.
 int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, int dense_rows,
                                   const void *w13, const void *w2, const int32_t *slot_of_expert,
                                   const void *row_scale, int R_cap, int H, int I, int S, void *hbuf,
                                   void *out, int32_t *status, cudaStream_t stream) {
-  if (sb_w13_interleaved())
+  if (!sb_w13_interleaved())
+    return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
+                                 H, I, S, hbuf, out, status, stream);
+  const int light = (tile_table != nullptr && H % 32 == 0 && I % 32 == 0) ? hybrid_rows() : 0;
+  if (light == 0)
     return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
-                                      R_cap, H, I, S, hbuf, out, status, stream);
-  return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
-                               H, I, S, hbuf, out, status, stream);
+                                      R_cap, H, I, S, hbuf, out, status, 0, stream);
+  std::lock_guard<std::mutex> lock(g_side_mu);
+  SideLane *lane = side_lane();
+  if (lane == nullptr) return fail(SB_E_CUDA, "sb_grouped_swiglu: cannot create the side stream");
+  SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
+  SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
+  int32_t rc = launch_decode_experts(rows, nullptr, 1, tile_table, slot_of_expert, w13, w2, row_scale, H, I, S,
+                                     hbuf, out, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status, 1,
+                                     lane->stream);
+  // the join is recorded even after a failed launch, so the side stream never
+  // stays forked from a stream that is being captured
+  SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
+  int32_t rc2 = SB_OK;
+  if (rc == SB_OK)
+    rc2 = launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
+                                     H, I, S, hbuf, out, status, light, stream);
+  SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
+  return rc != SB_OK ? rc : rc2;
 }
 
 // Carves the caller's workspace; the same walk gives the required size.
@@ -155,7 +216,7 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
                           void *shared_out, int32_t *status, void *stream) {
   return launch_decode_experts(x, item_of_slot, items_per_row, tile_table, slot_of_expert, w13, w2, row_scale,
                                H, I, n_slots, hbuf, y, shared_w13, shared_w2, shared_scale, I_shared, T,
-                               shared_h, shared_out, status, static_cast<cudaStream_t>(stream));
+                               shared_h, shared_out, status, 2, static_cast<cudaStream_t>(stream));
 }
 
 int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
@@ -224,7 +285,7 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     rc = launch_decode_experts(L->x, s.item_of_slot, K, s.tile_table, L->slot_of_expert, L->w13, L->w2,
                                s.slot_scale, H, I, L->n_slots, s.hbuf, s.y, Is > 0 ? L->shared_w13 : nullptr,
                                Is > 0 ? L->shared_w2 : nullptr, L->shared_gate_w ? s.shared_scale : nullptr,
-                               Is, T, s.shared_h, s.shared_out, status, stream);
+                               Is, T, s.shared_h, s.shared_out, status, 2, stream);
     if (rc != SB_OK) return rc;
     return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                           L->out, stream);

@@ -21,7 +21,10 @@
 // Two launches per layer, each covering the routed groups AND the shared
 // expert:  pass 1  h = bf16(bf16(silu(bf16 x.Wg)) * bf16 x.Wu)
 //          pass 2  y = bf16(bf16(h.Wd) * scale)
-// Routed token rows are read through `item_of_slot` (no gathered copy of x).
+// Routed token rows are read through `item_of_slot` (no gathered copy of x), or
+// directly when the rows are already expert-sorted (`item_of_slot` null).
+// Groups of more than 16 rows are left alone: next to the tile kernel this
+// pair of launches serves the light groups of a large batch.
 #include "sb_common.cuh"
 
 namespace sb {
@@ -115,7 +118,8 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
                       const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ w13,
                       int H, int I, int n_slots, int interleaved, __nv_bfloat16 *__restrict__ hbuf,
                       const __nv_bfloat16 *__restrict__ shared_w13, int I_sh, int T,
-                      __nv_bfloat16 *__restrict__ shared_h, int ks_n, int32_t *__restrict__ status) {
+                      __nv_bfloat16 *__restrict__ shared_h, int ks_n, int max_rows,
+                      int32_t *__restrict__ status) {
   __shared__ float red[kWarps][8][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -137,9 +141,9 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
       const int grp = (int)(rt / fb_routed);
       fb = (int)(rt - (long)grp * fb_routed);
       Group gr = read_group(tile_table, slot_of_expert, grp);
-      if (gr.slot == kSlotSkip) continue;
+      if (gr.slot == kSlotSkip || gr.end - gr.begin > max_rows) continue;   // larger groups belong to the tile kernel
       if (gr.slot < 0 || gr.slot >= n_slots) { if (status && threadIdx.x == 0) atomicExch(status, 2); continue; }
-      begin = gr.begin; end = min(gr.end, gr.begin + kMaxTok); inter = I;
+      begin = gr.begin; end = gr.end; inter = I;
       wbase = w13 + (size_t)gr.slot * 2 * I * H;
       out = hbuf;
     } else {
@@ -158,7 +162,7 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const int t = begin + max(0, min(nt * 8 + g, n_tok - 1));
-      const int row = is_shared ? t : (__ldg(item_of_slot + t) / items_per_row);
+      const int row = (is_shared || item_of_slot == nullptr) ? t : (__ldg(item_of_slot + t) / items_per_row);
       tok[nt] = x + (size_t)row * H + c * 8;
     }
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -192,7 +196,8 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
                    const __nv_bfloat16 *__restrict__ row_scale, int H, int I, int n_slots,
                    __nv_bfloat16 *__restrict__ y, const __nv_bfloat16 *__restrict__ shared_h,
                    const __nv_bfloat16 *__restrict__ shared_w2, const __nv_bfloat16 *__restrict__ shared_scale,
-                   int I_sh, int T, __nv_bfloat16 *__restrict__ shared_out, int ks_routed, int ks_shared) {
+                   int I_sh, int T, __nv_bfloat16 *__restrict__ shared_out, int ks_routed, int ks_shared,
+                   int max_rows) {
   __shared__ float red[kWarps][8][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -211,8 +216,8 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
       const int grp = (int)(rt / fb_routed);
       fb = (int)(rt - (long)grp * fb_routed);
       Group gr = read_group(tile_table, slot_of_expert, grp);
-      if (gr.slot < 0 || gr.slot >= n_slots) continue;          // skipped, or flagged by pass 1
-      begin = gr.begin; end = min(gr.end, gr.begin + kMaxTok); inter = I; ks_n = ks_routed;
+      if (gr.slot < 0 || gr.slot >= n_slots || gr.end - gr.begin > max_rows) continue;   // skipped, or flagged by pass 1
+      begin = gr.begin; end = gr.end; inter = I; ks_n = ks_routed;
       wmat = w2 + (size_t)gr.slot * H * I;
       hin = hbuf; scale = row_scale; out = y;
     } else {
@@ -272,33 +277,40 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
                               void *y, const void *shared_w13, const void *shared_w2, const void *shared_scale,
                               int I_sh, int T, void *shared_h, void *shared_out, int32_t *status,
-                              cudaStream_t stream) {
+                              int ctas_per_sm, cudaStream_t stream) {
   if (H % 32 != 0 || I % 32 != 0 || I_sh % 32 != 0)
     return fail(SB_E_UNSUPPORTED, "sb_decode_experts: H, I, I_shared must be multiples of 32");
-  if (T > kMaxTok) return fail(SB_E_UNSUPPORTED, "sb_decode_experts: at most SB_DECODE_MAX_TOKENS rows");
+  if (shared_w13 && T > kMaxTok)
+    return fail(SB_E_UNSUPPORTED, "sb_decode_experts: at most SB_DECODE_MAX_TOKENS rows for the shared expert");
   if (T <= 0) return SB_OK;
-  if (!x || (tile_table && (!item_of_slot || !w13 || !w2 || !hbuf || !y)))
+  if (!x || (tile_table && (!w13 || !w2 || !hbuf || !y)))
     return fail(SB_E_INVALID_ARG, "sb_decode_experts: null pointer");
   if ((shared_w13 != nullptr) != (shared_w2 != nullptr) || (shared_w13 && (!shared_h || !shared_out)))
     return fail(SB_E_INVALID_ARG, "sb_decode_experts: shared expert arguments go together");
   const int sms = sb_device_sm_count();
   if (sms <= 0) return fail(SB_E_CUDA, "sb_decode_experts: no CUDA device");
-  const int grid = sms * 2;       // two CTAs per SM, grid-stride over the block tasks
+  const int grid = sms * (ctas_per_sm == 1 ? 1 : 2);       // grid-stride over the block tasks
   // K slices per row group: about 16-22 chunks of 32 elements per warp
   auto slices = [](int k) { const int ch = k / 32; return ch > 96 ? 8 : ch > 48 ? 4 : ch > 24 ? 2 : 1; };
   const int ks1 = slices(H), ks2_routed = slices(I), ks2_shared = slices(I_sh > 0 ? I_sh : I);
+  // Next to the tile kernel (ctas_per_sm == 1) the SM must already be in the
+  // large-shared-memory configuration that kernel needs, or the two could not
+  // share an SM; alone, the default split leaves more L1 for the token rows.
+  const int carveout = ctas_per_sm == 1 ? (int)cudaSharedmemCarveoutMaxShared : (int)cudaSharedmemCarveoutDefault;
+  SB_CUDA_CHECK(cudaFuncSetAttribute(decode_gate_up_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, carveout));
+  SB_CUDA_CHECK(cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, carveout));
   decode_gate_up_kernel<<<grid, kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16 *>(x), item_of_slot, items_per_row, tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w13), H, I, n_slots, sb_w13_interleaved(),
       static_cast<__nv_bfloat16 *>(hbuf), static_cast<const __nv_bfloat16 *>(shared_w13), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_h), ks1, status);
+      static_cast<__nv_bfloat16 *>(shared_h), ks1, kMaxTok, status);
   SB_LAUNCH_CHECK();
   decode_down_kernel<<<grid, kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16 *>(hbuf), tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w2), static_cast<const __nv_bfloat16 *>(row_scale), H, I, n_slots,
       static_cast<__nv_bfloat16 *>(y), static_cast<const __nv_bfloat16 *>(shared_h),
       static_cast<const __nv_bfloat16 *>(shared_w2), static_cast<const __nv_bfloat16 *>(shared_scale), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared);
+      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, kMaxTok);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -189,37 +189,55 @@ __device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
   return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w));
 }
 
-// One CTA per token; rows come from the owners' output buffers.
+// One warp per token; rows come from the owners' output buffers.  Lanes 0..K-1
+// read the token's K (expert, owner rank, row) records and rank them by expert
+// id; then every lane fetches its 16-byte pieces of all K rows before the
+// first add, so the peer loads of a token are in flight together.
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(PeerPtrs y_rows, const int32_t *__restrict__ item_rank,
                   const int32_t *__restrict__ item_row, const int32_t *__restrict__ idx,
                   const uint4 *__restrict__ shared_out, int T, int vec_per_row, int K,
                   uint4 *__restrict__ out) {
-  __shared__ const uint4 *s_src[kMaxK];
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    if (threadIdx.x == 0) {
-      int eid[kMaxK]; const uint4 *src[kMaxK];
-      for (int k = 0; k < K; ++k) {
-        const int i = t * K + k;
-        const int e = idx[i], d = item_rank[i], r = item_row[i];
-        const uint4 *p = (d >= 0) ? static_cast<const uint4 *>(y_rows.p[d]) + (size_t)r * vec_per_row : nullptr;
-        int j = k;
-        while (j > 0 && eid[j - 1] > e) { eid[j] = eid[j - 1]; src[j] = src[j - 1]; --j; }
-        eid[j] = e; src[j] = p;
-      }
-      for (int k = 0; k < K; ++k) s_src[k] = src[k];
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * (blockDim.x >> 5);
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += warps_total) {
+    int e = 0x7fffffff;
+    unsigned long long ptr = 0;
+    if (lane < K) {
+      const int i = t * K + lane;
+      e = idx[i];
+      const int d = item_rank[i], r = item_row[i];
+      if (d >= 0) ptr = reinterpret_cast<unsigned long long>(static_cast<const uint4 *>(y_rows.p[d]) +
+                                                               (size_t)r * vec_per_row);
     }
-    __syncthreads();
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-      uint4 acc = make_uint4(0, 0, 0, 0);
-      for (int k = 0; k < K; ++k) {
-        const uint4 *p = s_src[k];
-        if (p != nullptr) acc = add8(acc, p[v]);
+    int pos = 0;                                      // position of this lane's row in expert-id order
+    for (int j = 0; j < K; ++j) {
+      const int ej = __shfl_sync(0xffffffffu, e, j);
+      pos += (ej < e || (ej == e && j < lane)) ? 1 : 0;
+    }
+    unsigned long long src[kMaxK];                    // row pointers in expert-id order, 0 = no row
+#pragma unroll
+    for (int k = 0; k < kMaxK; ++k) {
+      const unsigned who = __ballot_sync(0xffffffffu, lane < K && pos == k);
+      const unsigned long long p = __shfl_sync(0xffffffffu, ptr, who ? __ffs(who) - 1 : 0);
+      src[k] = who ? p : 0ull;
+    }
+    for (int v = lane; v < vec_per_row; v += 32) {
+      uint4 val[kMaxK];
+#pragma unroll
+      for (int k = 0; k < kMaxK; ++k) {
+        val[k] = make_uint4(0, 0, 0, 0);
+        if (src[k] != 0ull) val[k] = reinterpret_cast<const uint4 *>(src[k])[v];
       }
-      if (shared_out != nullptr) acc = add8(acc, __ldg(shared_out + (size_t)t * vec_per_row + v));
+      uint4 sh = make_uint4(0, 0, 0, 0);
+      if (shared_out != nullptr) sh = __ldg(shared_out + (size_t)t * vec_per_row + v);
+      uint4 acc = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < kMaxK; ++k)
+        if (src[k] != 0ull) acc = add8(acc, val[k]);
+      if (shared_out != nullptr) acc = add8(acc, sh);
       out[(size_t)t * vec_per_row + v] = acc;
     }
-    __syncthreads();
   }
 }
 
@@ -357,10 +375,10 @@ int32_t sb_ep_combine(void *const *peer_y, const int32_t *item_rank, const int32
   PeerPtrs py;
   int32_t rc = fill_peers(&py, peer_y, ep, "sb_ep_combine");
   if (rc != SB_OK) return rc;
-  int blocks = T;
-  const int max_blocks = sb_device_sm_count() * 16;
+  int blocks = (T + 7) / 8;                  // 8 warps per CTA, one token per warp
+  const int max_blocks = sb_device_sm_count() * 8;
   if (blocks > max_blocks) blocks = max_blocks;
-  const int threads = H / 8 >= 256 ? 256 : ((H / 8 + 31) / 32) * 32;
+  const int threads = 256;
   ep_combine_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       py, item_rank, item_row, idx, static_cast<const uint4 *>(shared_out), T, H / 8, K,
       static_cast<uint4 *>(out));

@@ -169,7 +169,7 @@ __device__ __forceinline__ uint32_t idesc_m256(int n) {
 struct Chunk { int slot, tok_begin, tok_end; };
 
 __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense_rows,
-                                            const int32_t *slot_of_expert, int c) {
+                                            const int32_t *slot_of_expert, int c, int skip_rows_upto) {
   Chunk t;
   if (tile_table == nullptr) {
     t.slot = 0;
@@ -180,6 +180,7 @@ __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense
     t.slot = slot_of_expert ? __ldg(slot_of_expert + e.x) : e.x;
     t.tok_begin = e.y;
     t.tok_end = e.z;
+    if (e.z - e.y <= skip_rows_upto) t.slot = kSlotSkip;      // light group: the streaming kernels' work
   }
   return t;
 }
@@ -191,7 +192,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                  const int32_t *__restrict__ tile_table, int dense_rows,
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
-                 int32_t *__restrict__ status) {
+                 int32_t *__restrict__ status, int skip_rows_upto) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -234,7 +235,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       bool ok = true;
       for (int tile = pair; ok && tile < total; tile += n_pairs) {
         const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c);
+        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto);
         if (ch.slot == kSlotSkip) continue;
         if (ch.slot < 0 || ch.slot >= n_slots) {
           if (status) atomicExch(status, 2);
@@ -266,7 +267,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < total; tile += n_pairs) {
-        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles);
+        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles, skip_rows_upto);
         if (ch.slot == kSlotSkip) continue;
         const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
         const uint32_t idesc = idesc_m256(n);
@@ -303,7 +304,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     int acc = 0; uint32_t acc_phase = 0;
     for (int tile = pair; tile < total; tile += n_pairs) {
       const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c);
+      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto);
       if (ch.slot == kSlotSkip) continue;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
       tc_fence_after();
@@ -418,14 +419,14 @@ int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, ui
 template <int MODE>
 int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
-                    int num_kb, int n_slots, int32_t *status, int grid, cudaStream_t stream) {
+                    int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto, cudaStream_t stream) {
   auto kern = pair_gemm_kernel<MODE>;
   SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
   kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
                                               slot_of_expert,
                                               static_cast<const __nv_bfloat16 *>(row_scale),
                                               static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
-                                              status);
+                                              status, skip_rows_upto);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -433,11 +434,12 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
 }  // namespace
 
 // w13 must be in the INTERLEAVED row order (row 2j = gate_j, row 2j+1 = up_j);
-// tile_table must have been built with 256-row tiles.
+// tile_table must have been built with 256-row tiles.  Tile entries of at most
+// `skip_rows_upto` rows are left to the caller (0 = none).
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
-                                   cudaStream_t stream) {
+                                   int skip_rows_upto, cudaStream_t stream) {
   if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
     return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
   if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
@@ -459,10 +461,10 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   const int grid = (sb_device_sm_count() / 2) * 2;
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
   rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
-                                H / kBlockK, S, status, grid, stream);
+                                H / kBlockK, S, status, grid, skip_rows_upto, stream);
   if (rc != SB_OK) return rc;
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
-                                 I / kBlockK, S, status, grid, stream);
+                                 I / kBlockK, S, status, grid, skip_rows_upto, stream);
 }
 
 }  // namespace sb

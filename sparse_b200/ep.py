@@ -305,6 +305,11 @@ class ExpertParallelLayer:
         self.bufs = bufs
         self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits)
         self.last_launches = 0
+        self.overlap = True
+        with torch.cuda.device(weights.device):
+            self._side = torch.cuda.Stream(device=weights.device)
+            self._fork = torch.cuda.Event()
+            self._join = torch.cuda.Event()
 
     @property
     def logits(self):
@@ -335,19 +340,37 @@ class ExpertParallelLayer:
                 marks.append((name, ev))
 
         with torch.cuda.device(r.device):
-            mark("begin")
-            r.stage_route(x)
-            mark("router+sort")
-            r.stage_publish()
-            self._barrier()
-            mark("publish+barrier")
-            r.stage_plan()
-            r.stage_dispatch()
-            mark("plan+dispatch")
-            r.stage_shared()
-            mark("shared_swiglu")
-            self._barrier()
-            mark("barrier(rows landed)")
+            if marks is not None or not self.overlap:
+                # one stream, stage after stage: what the per-stage timing marks measure
+                mark("begin")
+                r.stage_route(x)
+                mark("router+sort")
+                r.stage_publish()
+                self._barrier()
+                mark("publish+barrier")
+                r.stage_plan()
+                r.stage_dispatch()
+                mark("plan+dispatch")
+                r.stage_shared()
+                mark("shared_swiglu")
+                self._barrier()
+                mark("barrier(rows landed)")
+            else:
+                # The shared expert needs nothing from the peers: it runs on the
+                # caller's stream while count exchange, plan, dispatch and the
+                # "rows landed" barrier run beside it on the side stream.
+                r.stage_route(x)
+                r.stage_publish()
+                self._fork.record(stream)
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(self._fork)
+                    self._barrier()
+                    r.stage_plan()
+                    r.stage_dispatch()
+                    self._barrier()
+                    self._join.record(self._side)
+                r.stage_shared()
+                stream.wait_event(self._join)
             r.stage_experts()
             mark("routed_swiglu")
             self._barrier()
