@@ -96,6 +96,11 @@ class B200MoeBlock:
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
 
+    def host_pipeline(self, depth: int = 3) -> "HostPipeline":
+        """A queue for host-resident batches: copy-in, layer and copy-out of
+        successive batches overlap (see `HostPipeline`)."""
+        return HostPipeline(self, depth)
+
     def forward(self, hidden_states: torch.Tensor):
         b, s, h = hidden_states.shape
         x = hidden_states.reshape(-1, h)
@@ -118,3 +123,66 @@ class B200MoeBlock:
 
     def check_status(self) -> None:
         (self._ep or self.runner).check_status()
+
+
+class HostPipeline:
+    """Streams host batches through a block: batch i+1 is copied to the device
+    and batch i-1 is copied back while batch i is in the layer.
+
+    `submit(x_host, out_host)` enqueues one batch (pinned bf16 [T,H] buffers) and
+    returns at once; `out_host` is valid after `wait(ticket)` or `drain()`.  Each
+    of `depth` slots owns a device input and output buffer; a slot is reused only
+    after its copy-out has finished (an event wait on the copy-in stream, not a
+    host sync).  The layer itself runs on the stream that was current when the
+    pipeline was built."""
+
+    def __init__(self, block: B200MoeBlock, depth: int = 3):
+        if depth < 2:
+            raise ValueError("a pipeline needs at least 2 slots")
+        self.block = block
+        dev = block.device
+        t, h = block.runner.max_tokens, block.weights.hidden
+        with torch.cuda.device(dev):
+            self.compute = torch.cuda.current_stream(dev)
+            self.h2d = torch.cuda.Stream(device=dev)
+            self.d2h = torch.cuda.Stream(device=dev)
+            self.x_dev = [torch.empty((t, h), dtype=torch.bfloat16, device=dev) for _ in range(depth)]
+            self.out_dev = [torch.empty((t, h), dtype=torch.bfloat16, device=dev) for _ in range(depth)]
+            self.ev_in = [torch.cuda.Event() for _ in range(depth)]
+            self.ev_done = [torch.cuda.Event() for _ in range(depth)]
+            self.ev_out = [torch.cuda.Event() for _ in range(depth)]
+        self.depth = depth
+        self.count = 0
+
+    def submit(self, x_host: torch.Tensor, out_host: torch.Tensor) -> int:
+        t = x_host.shape[0]
+        if t > self.x_dev[0].shape[0]:
+            raise RuntimeError("pipeline was sized for %d rows, got %d" % (self.x_dev[0].shape[0], t))
+        slot = self.count % self.depth
+        xd, od = self.x_dev[slot][:t], self.out_dev[slot][:t]
+        if self.count >= self.depth:
+            self.h2d.wait_event(self.ev_out[slot])          # the slot's previous result has left the device
+        with torch.cuda.stream(self.h2d):
+            xd.copy_(x_host, non_blocking=True)
+            self.ev_in[slot].record(self.h2d)
+        self.compute.wait_event(self.ev_in[slot])
+        with torch.cuda.stream(self.compute):
+            self.block.forward_device(xd, od)
+            self.ev_done[slot].record(self.compute)
+        self.d2h.wait_event(self.ev_done[slot])
+        with torch.cuda.stream(self.d2h):
+            out_host.copy_(od, non_blocking=True)
+            self.ev_out[slot].record(self.d2h)
+        self.count += 1
+        return self.count - 1
+
+    def wait(self, ticket: int) -> None:
+        """Blocks until the result of `submit` number `ticket` is in its host buffer
+        (only the last `depth` tickets can still be waited for)."""
+        if ticket < self.count - self.depth or ticket >= self.count:
+            raise ValueError("ticket %d is not in flight" % ticket)
+        self.ev_out[ticket % self.depth].synchronize()
+
+    def drain(self) -> None:
+        self.d2h.synchronize()
+        self.compute.synchronize()
