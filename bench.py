@@ -42,10 +42,13 @@ WORKLOAD = "qwen1.5-moe-a2.7b-shaped MoE block, bf16, %d tokens/GPU, zipf(1.2) r
 CPU_SAMPLE_TOKENS = 512
 N_INPUT_BATCHES = 4          # rotated so a step never re-reads the previous step's activations
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
-# kernel (the gate/up pass of the routed grouped GEMM: 678.2 MB read + 44.7 MB
-# written), from the ncu capture summarised in profiles/grouped_gemm_qwen_t4096.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 722976256
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel
+# (pair_gemm_kernel), averaged over the four launches of one step (routed
+# gate/up 737.3 MB, routed down 412.5 MB, shared gate/up 106.6 MB, shared down
+# 73.6 MB = 1330.0 MB per step), from the ncu capture summarised in
+# profiles/pair_gemm_qwen_t4096.md.  The algorithmic bytes of the same four
+# launches are 1355.8 MB: nothing is re-read from DRAM.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 332502144
 
 
 def _peaks():
@@ -455,11 +458,12 @@ def run_ours(args):
         gemm_ms = stage_ms["routed_swiglu"] + stage_ms["shared_swiglu"]
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
         line["roofline"] = {
-            "bound": "tensor", "kernel": "grouped_gemm_kernel (tcgen05, 4 launches per step)",
+            "bound": "tensor", "kernel": "pair_gemm_kernel (tcgen05 cta_group::2; 4 launches per step, figures are per-launch averages)",
             "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_tflops"], "peak_source": "%s (burst cuBLAS bf16)" % peaks["source"],
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
             "flops_per_step": gemm_flops, "ms_per_step": gemm_ms,
+            "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
         }
         # whole-layer roofline per GPU: slower of dense compute at peak and
         # (HBM bytes at HBM peak + NVLink bytes at 900 GB/s per direction)
