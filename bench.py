@@ -426,6 +426,43 @@ def run_ours(args):
         ep_layer.stage_events = None
         recv_rows = int(ep_layer.r.recv_offsets[-1].item())
 
+    # ---- decode-sized steps through the same block (all ranks) ----
+    decode = {}
+    if not args.no_sweep:
+        for td in (1, 8, 16):
+            xd = [synth.make_hidden(td, shape.hidden, seed=900 + 31 * rank + b).to(torch.bfloat16).to(dev)
+                  for b in range(4)]
+            for i in range(5):
+                block.forward_device(xd[i % 4])
+            barrier()
+            n_dec = 100
+            ms = _time_region(lambda i: block.forward_device(xd[i % 4]), n_dec, stream)
+            barrier()
+            ms = max_over_ranks(ms) / n_dec
+            block.check_status()
+            # the same step captured once (4 passes over rotated inputs) and replayed
+            cap = torch.cuda.Stream(device=dev)
+            cap.wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap):
+                block.forward_device(xd[0])
+                with torch.cuda.graph(graph, stream=cap):
+                    for b in range(4):
+                        block.forward_device(xd[b])
+            stream.wait_stream(cap)
+            barrier()
+            for _ in range(3):
+                graph.replay()
+            barrier()
+            ms_g = _time_region(lambda i: graph.replay(), 25, stream)
+            barrier()
+            ms_g = max_over_ranks(ms_g) / 100
+            block.check_status()
+            decode[str(td)] = {"ms_per_layer": ms_g, "tokens_per_s": td * world / (ms_g * 1e-3),
+                               "tokens_per_gpu": td, "launches": block.last_launches,
+                               "launch_mode": "CUDA graph replay (4 layer passes per graph)",
+                               "eager_ms_per_layer": ms}
+
     if rank == 0:
         stages = {}
         if world == 1:
@@ -478,6 +515,8 @@ def run_ours(args):
                                   "distinct_experts": distinct,
                                   "nvlink_bytes_per_gpu_per_direction": nvlink_bytes,
                                   "nvlink_peak": "900 GB/s per direction (datasheet)"}
+        if decode:
+            line["decode"] = decode
         if world == 1 and not args.no_sweep:
             line["sweep"] = token_sweep(block.weights, shape, peaks)
         if world == 1 and not args.no_cpu_baseline:

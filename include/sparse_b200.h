@@ -203,18 +203,21 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
 /*
  * Decode-sized expert MLPs (a few tokens against whole expert matrices): the
  * same arithmetic as sb_grouped_swiglu for the routed groups of `tile_table`
- * AND the shared expert, as two weight-streaming launches on CUDA cores (one
- * warp per output feature).  Replaces the same reference spans as
- * sb_grouped_swiglu (utils/eval_core.py:11767-11793, 11765, 9455-9463) for
- * S == 1 decode steps.  Routed token rows are read through `item_of_slot`
- * (row = item / items_per_row of `x`), so sb_permute may be called with
- * out_rows == NULL.
+ * AND the shared expert, as two weight-streaming launches (each warp streams
+ * 16 weight rows through registers into warp-level MMAs).  Replaces the same
+ * reference spans as sb_grouped_swiglu (utils/eval_core.py:11767-11793, 11765,
+ * 9455-9463) for decode steps.  Routed token rows are read through
+ * `item_of_slot` (row = item / items_per_row of `x`), so sb_permute may be
+ * called with out_rows == NULL; with item_of_slot == NULL the rows of `x` are
+ * taken as already expert-sorted (row = position in the tile table's range).
  *
  *   x [T,H]; hbuf [n_items, I]; y [n_items, H]; shared_h [T, I_shared];
  *   shared_out [T, H]; row_scale [n_items] and shared_scale [T] bf16 or NULL;
  *   shared_w13 / shared_w2 NULL = no shared expert; tile_table NULL = no
  *   routed groups.  w13 row order as sb_w13_interleaved() says.
- * Limits: H, I, I_shared multiples of 8.
+ * Limits: H, I, I_shared multiples of 32; T <= SB_DECODE_MAX_TOKENS when there
+ * is a shared expert; routed groups of more than SB_DECODE_MAX_TOKENS rows are
+ * left untouched (sb_grouped_swiglu_mixed finishes those).
  */
 int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
                           const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
@@ -222,6 +225,43 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
                           void *hbuf, void *y, const void *shared_w13, const void *shared_w2,
                           const void *shared_scale, int32_t I_shared, int32_t T, void *shared_h,
                           void *shared_out, int32_t *status, void *stream);
+
+/*
+ * Expert MLPs for FEW rows per expert (decode-sized expert-parallel steps, where
+ * a rank receives a handful of rows for each of its experts): the routed groups
+ * of `tile_table` over already expert-sorted `rows`, plus (optionally) the shared
+ * expert over the rank's own `shared_x` [T,H], in the two weight-streaming
+ * launches of sb_decode_experts.  Groups are swept 16 rows at a time.
+ * `max_group_rows` is the caller's upper bound on the rows of any group (for an
+ * expert-parallel decode step: ep * tokens per rank); with 0 (unknown) only
+ * groups of at most SB_DECODE_MAX_TOKENS rows are streamed and the tensor-core
+ * kernel of sb_grouped_swiglu is launched for the rest.  Results as
+ * sb_grouped_swiglu up to fp32 summation order.  Replaces
+ * `_plain_ep_compute_segment` over the received segments and
+ * `_shared_expert_forward` (utils/eval_core.py:11700-11765, 13156-13372,
+ * 9455-9463) in decode.
+ */
+int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
+                                const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
+                                int32_t H, int32_t I, int32_t S, void *hbuf, void *out,
+                                int32_t max_group_rows, const void *shared_x, const void *shared_w13,
+                                const void *shared_w2, const void *shared_scale, int32_t I_shared, int32_t T,
+                                void *shared_h, void *shared_out, int32_t *status, void *stream);
+
+/*
+ * Decode-sized routing (T <= SB_DECODE_MAX_TOKENS, bf16): sb_router_topk and the
+ * sort half of sb_permute in two launches -- one warp per (token, router row),
+ * then softmax/top-k and the stable expert sort of the T*K items in a single
+ * CTA.  Same bits as sb_router_topk + sb_permute.  Replaces
+ * utils/eval_core.py:9519-9520, 9591-9595 and 14873-14882 for decode steps.
+ *   ws: T*E fp32 scratch; slot_scale [>= T*K] bf16 (route weight per sorted row);
+ *   the remaining outputs as in sb_router_topk / sb_permute.
+ */
+int32_t sb_route_decode(const void *x, const void *w_router, const float *router_bias, const void *w_shared_gate,
+                        int32_t T, int32_t H, int32_t E, int32_t K, int32_t renorm, int32_t fp32_logits,
+                        float *ws, int32_t *out_idx, void *out_w, void *out_logits, void *out_shared_scale,
+                        int32_t *expert_offsets, int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale,
+                        int32_t *tile_table, void *stream);
 
 /*
  * Un-permute and combine: for each token add its K expert rows in ascending
@@ -287,6 +327,15 @@ int32_t sb_ep_publish_counts(const int32_t *local_offsets, int32_t E, int32_t ra
 int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t epoch,
                       int32_t *status, void *stream);
 
+/* The same barrier with the epoch taken from (and advanced in) this rank's own
+ * device counter `epoch_counter` (uint32, zero at set-up, touched by nobody
+ * else): every rank issues the same sequence of barriers, so the counters move
+ * in step and no per-call value is baked into the launch -- a captured CUDA
+ * graph of a layer step can be replayed.  Do not mix with sb_ep_barrier on the
+ * same flags. */
+int32_t sb_ep_barrier_seq(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
+                          int32_t *status, void *stream);
+
 /* From the complete counts matrix: where this rank's items of each expert start
  * in the destination's receive buffer (`dst_base` [E]), and this rank's own
  * receive-side segments (`recv_offsets` [E+1], tile table as in sb_permute,
@@ -299,6 +348,28 @@ int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_
 int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, int32_t rank,
                    int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
                    int32_t *tile_table, void *stream);
+
+/* sb_ep_publish_counts + sb_ep_barrier_seq + sb_ep_plan as ONE single-CTA
+ * launch, for decode-sized steps where launches dominate (replaces the count
+ * all-to-all and host sync of utils/eval_core.py:14883-14911). */
+int32_t sb_ep_exchange_plan(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
+                            uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank, int32_t ep,
+                            int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets, int32_t *tile_table,
+                            int32_t *status, void *stream);
+
+/* The whole send side of a decode-sized step as ONE single-CTA launch:
+ * sb_ep_publish_counts, barrier, sb_ep_plan, sb_ep_dispatch, barrier ("every
+ * rank's rows have landed"); arguments as in those calls, `owner` the full
+ * [ep][E] table, two epochs taken from `epoch_counter`.  Meant for at most a
+ * few hundred items (one CTA copies the rows). */
+int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
+                                uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank,
+                                int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
+                                int32_t *tile_table, const void *x, const int32_t *item_expert,
+                                const void *item_scale, const int32_t *slot_of_item, int32_t n_items,
+                                int32_t items_per_row, int32_t H, void *const *peer_rows,
+                                void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
+                                int32_t *status, void *stream);
 
 /* Copy every item's activation row and route weight into its row of the
  * owner's receive buffers (`peer_rows[d]` [recv_cap,H] bf16, `peer_scale[d]`

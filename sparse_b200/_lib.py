@@ -57,6 +57,10 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_decode_experts": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32,
                                 vp, vp, vp, vp]),
+    "sb_grouped_swiglu_mixed": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp,
+                                      i32, i32, vp, vp, vp, vp]),
+    "sb_route_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                              vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
     "sb_peer_alloc": (i32, [sz, C.POINTER(vp)]),
@@ -66,6 +70,10 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ipc_close": (i32, [vp]),
     "sb_ep_publish_counts": (i32, [vp, i32, i32, i32, C.POINTER(vp), vp]),
     "sb_ep_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, vp, vp]),
+    "sb_ep_barrier_seq": (i32, [C.POINTER(vp), i32, i32, vp, vp, vp]),
+    "sb_ep_exchange_plan": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
+    "sb_ep_exchange_dispatch": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp,
+                                      vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp, vp, vp]),
     "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                              C.POINTER(vp), C.POINTER(vp), vp, vp, vp]),

@@ -39,7 +39,7 @@ struct SideLane {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
 };
-static std::mutex g_side_mu;
+static std::recursive_mutex g_side_mu;
 static SideLane g_side[64];
 
 static SideLane *side_lane() {
@@ -56,6 +56,14 @@ static SideLane *side_lane() {
     }
   }
   return &l;
+}
+
+static bool overlap_sort() {
+  static const bool v = [] {
+    const char *e = getenv("SPARSE_B200_OVERLAP_SORT");
+    return !(e && strcmp(e, "0") == 0);
+  }();
+  return v;
 }
 
 static int hybrid_rows() {
@@ -83,14 +91,14 @@ int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, i
   if (light == 0)
     return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
                                       R_cap, H, I, S, hbuf, out, status, 0, stream);
-  std::lock_guard<std::mutex> lock(g_side_mu);
+  std::lock_guard<std::recursive_mutex> lock(g_side_mu);
   SideLane *lane = side_lane();
   if (lane == nullptr) return fail(SB_E_CUDA, "sb_grouped_swiglu: cannot create the side stream");
   SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
   SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
   int32_t rc = launch_decode_experts(rows, nullptr, 1, tile_table, slot_of_expert, w13, w2, row_scale, H, I, S,
-                                     hbuf, out, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status, 1,
-                                     lane->stream);
+                                     hbuf, out, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status, 1, 0,
+                                     nullptr, lane->stream);
   // the join is recorded even after a failed launch, so the side stream never
   // stays forked from a stream that is being captured
   SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
@@ -214,9 +222,56 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
                           void *hbuf, void *y, const void *shared_w13, const void *shared_w2,
                           const void *shared_scale, int32_t I_shared, int32_t T, void *shared_h,
                           void *shared_out, int32_t *status, void *stream) {
+  if (shared_w13 && T > SB_DECODE_MAX_TOKENS)
+    return fail(SB_E_UNSUPPORTED, "sb_decode_experts: at most %d rows for the shared expert", SB_DECODE_MAX_TOKENS);
   return launch_decode_experts(x, item_of_slot, items_per_row, tile_table, slot_of_expert, w13, w2, row_scale,
                                H, I, n_slots, hbuf, y, shared_w13, shared_w2, shared_scale, I_shared, T,
-                               shared_h, shared_out, status, 2, static_cast<cudaStream_t>(stream));
+                               shared_h, shared_out, status, 2, 0, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
+                                const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
+                                int32_t H, int32_t I, int32_t S, void *hbuf, void *out,
+                                int32_t max_group_rows, const void *shared_x, const void *shared_w13,
+                                const void *shared_w2, const void *shared_scale, int32_t I_shared, int32_t T,
+                                void *shared_h, void *shared_out, int32_t *status, void *stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!tile_table) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: needs a tile table");
+  const bool with_shared = shared_w13 != nullptr && T > 0;
+  if (with_shared && (!shared_x || !shared_w2 || !shared_h || !shared_out || I_shared <= 0))
+    return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: shared expert arguments go together");
+  if (!sb_w13_interleaved() || H % 32 != 0 || I % 32 != 0 || (with_shared && I_shared % 32 != 0)) {
+    int32_t rc = launch_grouped_swiglu_any(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S,
+                                           hbuf, out, status, st);
+    if (rc != SB_OK || !with_shared) return rc;
+    return launch_grouped_swiglu_any(shared_x, nullptr, T, shared_w13, shared_w2, nullptr, shared_scale, T, H,
+                                     I_shared, 1, shared_h, shared_out, status, st);
+  }
+  const int limit = max_group_rows > 0 ? max_group_rows : SB_DECODE_MAX_TOKENS;
+  int32_t rc = launch_decode_experts(rows, nullptr, 1, tile_table, slot_of_expert, w13, w2, row_scale, H, I, S,
+                                     hbuf, out, with_shared ? shared_w13 : nullptr,
+                                     with_shared ? shared_w2 : nullptr, with_shared ? shared_scale : nullptr,
+                                     with_shared ? I_shared : 0, with_shared ? T : 1, shared_h, shared_out,
+                                     status, 2, limit, shared_x, st);
+  if (rc != SB_OK || max_group_rows > 0) return rc;     // the caller's bound says no group is left over
+  return launch_grouped_swiglu_pair(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S,
+                                    hbuf, out, status, limit, st);
+}
+
+int32_t sb_route_decode(const void *x, const void *w_router, const float *router_bias, const void *w_shared_gate,
+                        int32_t T, int32_t H, int32_t E, int32_t K, int32_t renorm, int32_t fp32_logits,
+                        float *ws, int32_t *out_idx, void *out_w, void *out_logits, void *out_shared_scale,
+                        int32_t *expert_offsets, int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale,
+                        int32_t *tile_table, void *stream) {
+  if (T < 0 || T > SB_DECODE_MAX_TOKENS)
+    return fail(SB_E_INVALID_ARG, "sb_route_decode: T=%d outside [0,%d]", T, SB_DECODE_MAX_TOKENS);
+  if (!x || !w_router || !out_idx || !out_w || !tile_table)
+    return fail(SB_E_INVALID_ARG, "sb_route_decode: null pointer");
+  if ((w_shared_gate != nullptr) != (out_shared_scale != nullptr))
+    return fail(SB_E_INVALID_ARG, "sb_route_decode: w_shared_gate and out_shared_scale go together");
+  return launch_router_decode(x, w_router, router_bias, w_shared_gate, T, H, E, K, renorm, fp32_logits, ws,
+                              out_idx, out_w, out_logits, out_shared_scale, expert_offsets, slot_of_item,
+                              item_of_slot, slot_scale, tile_table, static_cast<cudaStream_t>(stream));
 }
 
 int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
@@ -285,24 +340,44 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     rc = launch_decode_experts(L->x, s.item_of_slot, K, s.tile_table, L->slot_of_expert, L->w13, L->w2,
                                s.slot_scale, H, I, L->n_slots, s.hbuf, s.y, Is > 0 ? L->shared_w13 : nullptr,
                                Is > 0 ? L->shared_w2 : nullptr, L->shared_gate_w ? s.shared_scale : nullptr,
-                               Is, T, s.shared_h, s.shared_out, status, 2, stream);
+                               Is, T, s.shared_h, s.shared_out, status, 2, 0, nullptr, stream);
     if (rc != SB_OK) return rc;
     return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                           L->out, stream);
   }
+  // The shared expert needs nothing from the sort: it runs on the caller's
+  // stream while count/scan/scatter/gather (one busy SM, then a short copy) run
+  // beside it on the library's side stream; the routed GEMM waits for both.
+  SideLane *lane = nullptr;
+  std::unique_lock<std::recursive_mutex> lock(g_side_mu, std::defer_lock);
+  if (Is > 0 && overlap_sort()) {
+    lock.lock();
+    lane = side_lane();
+  }
+  cudaStream_t sort_stream = stream;
+  if (lane != nullptr) {
+    SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
+    SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
+    sort_stream = lane->stream;
+  }
   rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes,
                       s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
-                      s.tile_table, stream);
-  if (rc != SB_OK) return rc;
-  rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
-                             s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
-  if (rc != SB_OK) return rc;
-  if (Is > 0) {
-    rc = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
-                               L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
-                               s.shared_out, status, stream);
-    if (rc != SB_OK) return rc;
+                      s.tile_table, sort_stream);
+  if (lane != nullptr) SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
+  int32_t rc_shared = SB_OK;
+  if (rc == SB_OK && Is > 0)
+    rc_shared = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
+                                          L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
+                                          s.shared_out, status, stream);
+  if (lane != nullptr) {
+    SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
+    lock.unlock();
   }
+  if (rc != SB_OK) return rc;
+  if (rc_shared != SB_OK) return rc_shared;
+  rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
+                                 s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
+  if (rc != SB_OK) return rc;
   return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                         L->out, stream);
 }

@@ -117,6 +117,7 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
                       int items_per_row, const int32_t *__restrict__ tile_table,
                       const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ w13,
                       int H, int I, int n_slots, int interleaved, __nv_bfloat16 *__restrict__ hbuf,
+                      const __nv_bfloat16 *__restrict__ shared_x,
                       const __nv_bfloat16 *__restrict__ shared_w13, int I_sh, int T,
                       __nv_bfloat16 *__restrict__ shared_h, int ks_n, int max_rows,
                       int32_t *__restrict__ status) {
@@ -148,22 +149,28 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
       out = hbuf;
     } else {
       fb = (int)task_id;
-      begin = 0; end = min(T, kMaxTok); inter = I_sh;
+      begin = 0; end = T; inter = I_sh;
       wbase = shared_w13;
       out = shared_h;
     }
-    const int n_tok = end - begin;
     const int f0 = fb * feats + rg * 8;
-    const bool live = f0 < inter && n_tok > 0;
     const int f = min(f0 + g, inter - 1);
     const __nv_bfloat16 *row_lo = wbase + (size_t)(interleaved ? 2 * f : f) * H + c * 8;
     const __nv_bfloat16 *row_hi = wbase + (size_t)(interleaved ? 2 * f + 1 : inter + f) * H + c * 8;
+    const __nv_bfloat16 *xrows = is_shared ? shared_x : x;
+    // groups of more than 16 rows are swept 16 rows at a time (the weights of
+    // the later sweeps come from L2)
+    const int group_end = end;
+    for (; begin < group_end; begin += kMaxTok) {
+    end = min(group_end, begin + kMaxTok);
+    const int n_tok = end - begin;
+    const bool live = f0 < inter && n_tok > 0;
     const __nv_bfloat16 *tok[2];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const int t = begin + max(0, min(nt * 8 + g, n_tok - 1));
       const int row = (is_shared || item_of_slot == nullptr) ? t : (__ldg(item_of_slot + t) / items_per_row);
-      tok[nt] = x + (size_t)row * H + c * 8;
+      tok[nt] = xrows + (size_t)row * H + c * 8;
     }
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     if (live) {
@@ -183,6 +190,7 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
             out[(size_t)(begin + t) * inter + f0 + g] = __float2bfloat16_rn(sv * uv);
           }
         }
+    }
     }
   }
 }
@@ -222,19 +230,22 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
       hin = hbuf; scale = row_scale; out = y;
     } else {
       fb = (int)task_id;
-      begin = 0; end = min(T, kMaxTok); inter = I_sh; ks_n = ks_shared;
+      begin = 0; end = T; inter = I_sh; ks_n = ks_shared;
       wmat = shared_w2;
       hin = shared_h; scale = shared_scale; out = shared_out;
     }
     const int rg = warp / ks_n, ks = warp % ks_n;
-    const int n_tok = end - begin;
     const int n0 = (fb * (kWarps / ks_n) + rg) * 16;
-    const bool live = n0 < H && n_tok > 0;
     const int chunks = inter / 32, per = (chunks + ks_n - 1) / ks_n;
     const int ch0 = min(chunks, ks * per), ch1 = min(chunks, ch0 + per);
     const int r_lo = min(n0 + g, H - 1), r_hi = min(n0 + 8 + g, H - 1);
     const __nv_bfloat16 *row_lo = wmat + (size_t)r_lo * inter + c * 8;
     const __nv_bfloat16 *row_hi = wmat + (size_t)r_hi * inter + c * 8;
+    const int group_end = end;
+    for (; begin < group_end; begin += kMaxTok) {
+    end = min(group_end, begin + kMaxTok);
+    const int n_tok = end - begin;
+    const bool live = n0 < H && n_tok > 0;
     const __nv_bfloat16 *tok[2];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
@@ -267,6 +278,7 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
           }
         }
     }
+    }
   }
 }
 
@@ -277,11 +289,11 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
                               void *y, const void *shared_w13, const void *shared_w2, const void *shared_scale,
                               int I_sh, int T, void *shared_h, void *shared_out, int32_t *status,
-                              int ctas_per_sm, cudaStream_t stream) {
+                              int ctas_per_sm, int max_rows, const void *shared_x, cudaStream_t stream) {
   if (H % 32 != 0 || I % 32 != 0 || I_sh % 32 != 0)
     return fail(SB_E_UNSUPPORTED, "sb_decode_experts: H, I, I_shared must be multiples of 32");
-  if (shared_w13 && T > kMaxTok)
-    return fail(SB_E_UNSUPPORTED, "sb_decode_experts: at most SB_DECODE_MAX_TOKENS rows for the shared expert");
+  if (max_rows <= 0) max_rows = kMaxTok;
+  if (shared_x == nullptr) shared_x = x;
   if (T <= 0) return SB_OK;
   if (!x || (tile_table && (!w13 || !w2 || !hbuf || !y)))
     return fail(SB_E_INVALID_ARG, "sb_decode_experts: null pointer");
@@ -302,15 +314,16 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
   decode_gate_up_kernel<<<grid, kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16 *>(x), item_of_slot, items_per_row, tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w13), H, I, n_slots, sb_w13_interleaved(),
-      static_cast<__nv_bfloat16 *>(hbuf), static_cast<const __nv_bfloat16 *>(shared_w13), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_h), ks1, kMaxTok, status);
+      static_cast<__nv_bfloat16 *>(hbuf), static_cast<const __nv_bfloat16 *>(shared_x),
+      static_cast<const __nv_bfloat16 *>(shared_w13), I_sh, T,
+      static_cast<__nv_bfloat16 *>(shared_h), ks1, max_rows, status);
   SB_LAUNCH_CHECK();
   decode_down_kernel<<<grid, kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16 *>(hbuf), tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w2), static_cast<const __nv_bfloat16 *>(row_scale), H, I, n_slots,
       static_cast<__nv_bfloat16 *>(y), static_cast<const __nv_bfloat16 *>(shared_h),
       static_cast<const __nv_bfloat16 *>(shared_w2), static_cast<const __nv_bfloat16 *>(shared_scale), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, kMaxTok);
+      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, max_rows);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

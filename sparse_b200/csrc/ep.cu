@@ -53,8 +53,8 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 }
 
 // counts_all on every rank: [ep][E]; this rank fills row `rank` everywhere.
-__global__ void ep_publish_kernel(const int32_t *__restrict__ local_offsets, int E, int rank, int ep,
-                                  PeerPtrs counts_all) {
+__device__ __forceinline__ void publish_body(const int32_t *__restrict__ local_offsets, int E, int rank, int ep,
+                                             const PeerPtrs &counts_all) {
   for (int i = threadIdx.x; i < E * ep; i += blockDim.x) {
     int p = i / E, e = i - p * E;
     int32_t *dst = static_cast<int32_t *>(counts_all.p[p]) + (size_t)rank * E + e;
@@ -62,8 +62,15 @@ __global__ void ep_publish_kernel(const int32_t *__restrict__ local_offsets, int
   }
 }
 
-__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epoch,
-                                  int32_t *__restrict__ status) {
+__global__ void ep_publish_kernel(const int32_t *__restrict__ local_offsets, int E, int rank, int ep,
+                                  PeerPtrs counts_all) {
+  publish_body(local_offsets, E, rank, ep, counts_all);
+}
+
+// Thread p < ep tells peer p "this rank reached `epoch`" and waits for peer p's
+// flag to reach it; the wait is bounded.
+__device__ __forceinline__ void barrier_body(const PeerPtrs &flags, int rank, int ep, uint32_t epoch,
+                                             int32_t *__restrict__ status) {
   const int p = threadIdx.x;
   if (p >= ep) return;
   __threadfence_system();
@@ -84,17 +91,33 @@ __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epo
   __threadfence_system();
 }
 
+// The epoch of a barrier that takes it from this rank's device counter: every
+// rank runs the same sequence of barriers, so the counters advance in step and
+// a captured CUDA graph can be replayed (no epoch baked into the launch).
+__device__ __forceinline__ uint32_t next_epoch(uint32_t *counter) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) { s_epoch = *counter + 1u; *counter = s_epoch; }
+  __syncthreads();
+  return s_epoch;
+}
+
+__global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epoch, uint32_t *epoch_counter,
+                                  int32_t *__restrict__ status) {
+  if (epoch_counter != nullptr) epoch = next_epoch(epoch_counter);
+  barrier_body(flags, rank, ep, epoch, status);
+}
+
 // One CTA.  Reads the complete counts matrix of this rank and writes
 //   dst_base[e]  first row, in the destination's receive buffer, of THIS rank's items of expert e
 //   recv_offsets[E+1], tile table: this rank's receive-side expert segments
 // `owner` is the destination table [ep][E]: owner[s][e] = rank that executes
 // expert e for tokens on rank s (one row repeated for plain ownership, different
 // rows when hot experts are replicated and sources are spread over the replicas).
-__global__ void __launch_bounds__(256)
-ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict__ owner, int E,
-               int rank, int ep, int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
-               int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table) {
-  extern __shared__ int plan_smem[];
+__device__ __forceinline__ void plan_body(const volatile int32_t *counts_all,
+                                          const int32_t *__restrict__ owner, int E, int rank, int ep,
+                                          int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
+                                          int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table,
+                                          int *plan_smem) {
   int *tot = plan_smem;                    // [ep][E] rows of expert e arriving at rank d
   int *seg = tot + ep * E;                 // [ep][E] first row of expert e in rank d's buffer
   int *my_off = seg + ep * E;              // [E+1]
@@ -149,17 +172,45 @@ ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict
   }
 }
 
-// One warp per item: activation row and route weight to the owner's buffer.
 __global__ void __launch_bounds__(256)
-ep_dispatch_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item_expert,
-                   const __nv_bfloat16 *__restrict__ item_scale,
-                   const int32_t *__restrict__ slot_of_item, const int32_t *__restrict__ local_offsets,
-                   const int32_t *__restrict__ dst_base, const int32_t *__restrict__ owner,
-                   int n_items, int items_per_row, int vec_per_row, int recv_cap, PeerPtrs recv_rows,
-                   PeerPtrs recv_scale, int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row) {
+ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict__ owner, int E,
+               int rank, int ep, int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
+               int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table) {
+  extern __shared__ int plan_smem[];
+  plan_body(counts_all, owner, E, rank, ep, tile_cap, tile_rows, dst_base, recv_offsets, tile_table, plan_smem);
+}
+
+// publish + barrier + plan in one single-CTA launch (the decode-sized step is
+// launch-bound): counts go out to every peer, the barrier makes all rows of the
+// local counts matrix valid, the plan is derived from it.
+__global__ void __launch_bounds__(256)
+ep_exchange_plan_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs counts_all, PeerPtrs flags,
+                        uint32_t *epoch_counter, const int32_t *__restrict__ owner, int E, int rank, int ep,
+                        int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
+                        int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table,
+                        int32_t *__restrict__ status) {
+  extern __shared__ int plan_smem[];
+  publish_body(local_offsets, E, rank, ep, counts_all);
+  __threadfence_system();
+  const uint32_t epoch = next_epoch(epoch_counter);      // its __syncthreads also orders the stores above
+  barrier_body(flags, rank, ep, epoch, status);
+  __syncthreads();
+  plan_body(static_cast<const int32_t *>(counts_all.p[rank]), owner, E, rank, ep, tile_cap, tile_rows, dst_base,
+            recv_offsets, tile_table, plan_smem);
+}
+
+// One warp per item: activation row and route weight to the owner's buffer.
+__device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const int32_t *__restrict__ item_expert,
+                                              const __nv_bfloat16 *__restrict__ item_scale,
+                                              const int32_t *__restrict__ slot_of_item,
+                                              const int32_t *__restrict__ local_offsets,
+                                              const volatile int32_t *dst_base, const int32_t *__restrict__ owner,
+                                              int n_items, int items_per_row, int vec_per_row, int recv_cap,
+                                              const PeerPtrs &recv_rows, const PeerPtrs &recv_scale,
+                                              int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
+                                              int first_warp, int warps_total) {
   const int lane = threadIdx.x & 31;
-  const int warps_total = gridDim.x * (blockDim.x >> 5);
-  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n_items; i += warps_total) {
+  for (int i = first_warp; i < n_items; i += warps_total) {
     const int e = item_expert[i];
     const int slot = slot_of_item[i];
     if (e < 0 || slot < 0) {
@@ -180,6 +231,48 @@ ep_dispatch_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item
       item_rank[i] = d; item_row[i] = row;
     }
   }
+}
+
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item_expert,
+                   const __nv_bfloat16 *__restrict__ item_scale,
+                   const int32_t *__restrict__ slot_of_item, const int32_t *__restrict__ local_offsets,
+                   const int32_t *__restrict__ dst_base, const int32_t *__restrict__ owner,
+                   int n_items, int items_per_row, int vec_per_row, int recv_cap, PeerPtrs recv_rows,
+                   PeerPtrs recv_scale, int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row) {
+  dispatch_body(x, item_expert, item_scale, slot_of_item, local_offsets, dst_base, owner, n_items, items_per_row,
+                vec_per_row, recv_cap, recv_rows, recv_scale, item_rank, item_row,
+                blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), gridDim.x * (blockDim.x >> 5));
+}
+
+// The whole send side of a decode-sized step in ONE single-CTA launch: counts
+// out, barrier, plan, rows out, barrier ("rows landed").  A few dozen rows are
+// a few hundred KB; the launches this saves cost more than the copy.
+__global__ void __launch_bounds__(256)
+ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs counts_all, PeerPtrs flags,
+                            uint32_t *epoch_counter, const int32_t *__restrict__ owner, int E, int rank, int ep,
+                            int tile_cap, int tile_rows, int32_t *dst_base, int32_t *__restrict__ recv_offsets,
+                            int32_t *__restrict__ tile_table, const uint4 *__restrict__ x,
+                            const int32_t *__restrict__ item_expert, const __nv_bfloat16 *__restrict__ item_scale,
+                            const int32_t *__restrict__ slot_of_item, int n_items, int items_per_row,
+                            int vec_per_row, int recv_cap, PeerPtrs recv_rows, PeerPtrs recv_scale,
+                            int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
+                            int32_t *__restrict__ status) {
+  extern __shared__ int plan_smem[];
+  publish_body(local_offsets, E, rank, ep, counts_all);
+  __threadfence_system();
+  uint32_t epoch = next_epoch(epoch_counter);
+  barrier_body(flags, rank, ep, epoch, status);
+  __syncthreads();
+  plan_body(static_cast<const int32_t *>(counts_all.p[rank]), owner, E, rank, ep, tile_cap, tile_rows, dst_base,
+            recv_offsets, tile_table, plan_smem);
+  __syncthreads();                      // dst_base (global, written by this CTA) is visible to all its threads
+  dispatch_body(x, item_expert, item_scale, slot_of_item, local_offsets, dst_base, owner + (size_t)rank * E,
+                n_items, items_per_row, vec_per_row, recv_cap, recv_rows, recv_scale, item_rank, item_row,
+                threadIdx.x >> 5, blockDim.x >> 5);
+  __threadfence_system();
+  epoch = next_epoch(epoch_counter);
+  barrier_body(flags, rank, ep, epoch, status);
 }
 
 __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
@@ -316,7 +409,76 @@ int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_
   PeerPtrs pf;
   int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier");
   if (rc != SB_OK) return rc;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, epoch, status);
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, epoch, nullptr, status);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_barrier_seq(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
+                          int32_t *status, void *stream) {
+  if (rank < 0 || rank >= ep || !epoch_counter)
+    return fail(SB_E_INVALID_ARG, "sb_ep_barrier_seq: rank=%d ep=%d", rank, ep);
+  PeerPtrs pf;
+  int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier_seq");
+  if (rc != SB_OK) return rc;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, 0u, epoch_counter, status);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_exchange_plan(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
+                            uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank, int32_t ep,
+                            int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets, int32_t *tile_table,
+                            int32_t *status, void *stream) {
+  if (!local_offsets || !epoch_counter || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 ||
+      E > kMaxExperts || rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_plan: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
+  PeerPtrs pc, pf;
+  int32_t rc = fill_peers(&pc, peer_counts, ep, "sb_ep_exchange_plan");
+  if (rc != SB_OK) return rc;
+  if ((rc = fill_peers(&pf, peer_flags, ep, "sb_ep_exchange_plan")) != SB_OK) return rc;
+  const int tile_cap = recv_cap / SB_TILE_M + E;
+  const size_t smem = ((size_t)2 * ep * E + 2 * (size_t)(E + 1)) * sizeof(int);
+  if (smem > 48 * 1024)
+    SB_CUDA_CHECK(cudaFuncSetAttribute(ep_exchange_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+  ep_exchange_plan_kernel<<<1, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      local_offsets, pc, pf, epoch_counter, owner, E, rank, ep, tile_cap, sb_tile_rows(), dst_base,
+      recv_offsets, tile_table, status);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
+                                uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank,
+                                int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
+                                int32_t *tile_table, const void *x, const int32_t *item_expert,
+                                const void *item_scale, const int32_t *slot_of_item, int32_t n_items,
+                                int32_t items_per_row, int32_t H, void *const *peer_rows,
+                                void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
+                                int32_t *status, void *stream) {
+  if (!local_offsets || !epoch_counter || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 ||
+      E > kMaxExperts || rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
+  if (n_items < 0 || H % 8 != 0 || items_per_row < 1)
+    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: bad arguments (n_items=%d H=%d)", n_items, H);
+  if (n_items > 0 && (!x || !item_expert || !item_scale || !slot_of_item || !item_rank || !item_row))
+    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: null pointer");
+  PeerPtrs pc, pf, pr, ps;
+  int32_t rc;
+  if ((rc = fill_peers(&pc, peer_counts, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  if ((rc = fill_peers(&pf, peer_flags, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  if ((rc = fill_peers(&pr, peer_rows, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  if ((rc = fill_peers(&ps, peer_scale, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  const int tile_cap = recv_cap / SB_TILE_M + E;
+  const size_t smem = ((size_t)2 * ep * E + 2 * (size_t)(E + 1)) * sizeof(int);
+  if (smem > 48 * 1024)
+    SB_CUDA_CHECK(cudaFuncSetAttribute(ep_exchange_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+  ep_exchange_dispatch_kernel<<<1, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      local_offsets, pc, pf, epoch_counter, owner, E, rank, ep, tile_cap, sb_tile_rows(), dst_base, recv_offsets,
+      tile_table, static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),
+      slot_of_item, n_items, items_per_row, H / 8, recv_cap, pr, ps, item_rank, item_row, status);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -422,6 +422,10 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
                     int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto, cudaStream_t stream) {
   auto kern = pair_gemm_kernel<MODE>;
   SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  // ask for the largest shared-memory split so that small kernels of other
+  // streams (router, sort, gather) can share an SM with a resident GEMM CTA
+  SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
   kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
                                               slot_of_expert,
                                               static_cast<const __nv_bfloat16 *>(row_scale),

@@ -89,7 +89,8 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
                               void *y, const void *shared_w13, const void *shared_w2,
                               const void *shared_scale, int I_sh, int T, void *shared_h, void *shared_out,
-                              int32_t *status, int ctas_per_sm, cudaStream_t stream);
+                              int32_t *status, int ctas_per_sm, int max_rows, const void *shared_x,
+                              cudaStream_t stream);
 int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
                        const void *shared_out, int T, int H, int K, void *out,
                        cudaStream_t stream);

@@ -98,6 +98,8 @@ class PeerBuffers:
             "ctl": _round_up(ep * num_experts * 4, 256) + 256,
         }
         self.flags_offset = _round_up(ep * num_experts * 4, 256)
+        # this rank's barrier epoch counter (uint32, touched by no peer) sits behind the flags
+        self.epoch_offset = self.flags_offset + 128
         self.local = {}
         self.peers = {n: [0] * ep for n in self.NAMES}
         self._owned: List[int] = []
@@ -198,9 +200,17 @@ class EpRank:
         self.launches = 0
         self._x = None
         self._t = 0
+        # Batches of at most DECODE_MAX_TOKENS rows take the decode-sized kernels
+        # (per-row router, single-CTA sort, weight-streaming expert kernels).
+        self.small_batch_kernels = True
+        self.route_ws = torch.empty((_lib.DECODE_MAX_TOKENS * e,), dtype=torch.float32, device=dev)
+        self.local_scale = torch.empty((max(_lib.DECODE_MAX_TOKENS * top_k, 1),), dtype=bf, device=dev)
 
     def _s(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _small(self) -> bool:
+        return self.small_batch_kernels and 0 < self._t <= _lib.DECODE_MAX_TOKENS
 
     # -- stages -------------------------------------------------------------------
     def stage_route(self, x: torch.Tensor) -> None:
@@ -208,6 +218,19 @@ class EpRank:
         if t > self.max_tokens:
             raise RuntimeError("EP layer was sized for %d tokens, got %d" % (self.max_tokens, t))
         self._x, self._t = x, t
+        if self._small():
+            check(lib.sb_route_decode(
+                x.data_ptr(), w.router_w.data_ptr(),
+                w.router_bias.data_ptr() if w.router_bias is not None else None,
+                w.shared_gate_w.data_ptr() if w.shared_gate_w is not None else None,
+                t, w.hidden, w.num_experts, k, int(self.renorm), int(self.fp32_logits),
+                self.route_ws.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(),
+                self.logits.data_ptr(),
+                self.shared_scale.data_ptr() if w.shared_gate_w is not None else None,
+                self.local_offsets.data_ptr(), self.slot_of_item.data_ptr(), self.item_of_slot.data_ptr(),
+                self.local_scale.data_ptr(), self.local_tiles.data_ptr(), self._s()), "sb_route_decode")
+            self.launches += 2
+            return
         check(lib.sb_router_topk(
             x.data_ptr(), w.router_w.data_ptr(),
             w.router_bias.data_ptr() if w.router_bias is not None else None,
@@ -229,10 +252,50 @@ class EpRank:
               "sb_ep_publish_counts")
         self.launches += 1
 
-    def stage_barrier(self, epoch: int) -> None:
-        check(lib.sb_ep_barrier(self.bufs.ptr_array("ctl", self.bufs.flags_offset), self.rank, self.ep,
-                                epoch, self.status.data_ptr(), self._s()), "sb_ep_barrier")
+    def stage_barrier(self) -> None:
+        b = self.bufs
+        check(lib.sb_ep_barrier_seq(b.ptr_array("ctl", b.flags_offset), self.rank, self.ep,
+                                    b.local["ctl"] + b.epoch_offset, self.status.data_ptr(), self._s()),
+              "sb_ep_barrier_seq")
         self.launches += 1
+
+    def stage_exchange_plan(self) -> None:
+        """publish + barrier + plan as one launch."""
+        b = self.bufs
+        check(lib.sb_ep_exchange_plan(
+            self.local_offsets.data_ptr(), b.ptr_array("ctl"), b.ptr_array("ctl", b.flags_offset),
+            b.local["ctl"] + b.epoch_offset, self.owner.data_ptr(), self.w.num_experts, self.rank, self.ep,
+            b.recv_cap, self.dst_base.data_ptr(), self.recv_offsets.data_ptr(), self.recv_tiles.data_ptr(),
+            self.status.data_ptr(), self._s()), "sb_ep_exchange_plan")
+        self.launches += 1
+
+    def stage_exchange_dispatch(self) -> None:
+        """publish + barrier + plan + dispatch + barrier as one launch (decode-sized steps)."""
+        b, w, t, k = self.bufs, self.w, self._t, self.top_k
+        check(lib.sb_ep_exchange_dispatch(
+            self.local_offsets.data_ptr(), b.ptr_array("ctl"), b.ptr_array("ctl", b.flags_offset),
+            b.local["ctl"] + b.epoch_offset, self.owner.data_ptr(), w.num_experts, self.rank, self.ep,
+            b.recv_cap, self.dst_base.data_ptr(), self.recv_offsets.data_ptr(), self.recv_tiles.data_ptr(),
+            self._x.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(), self.slot_of_item.data_ptr(),
+            t * k, k, w.hidden, b.ptr_array("rows"), b.ptr_array("scale"), self.item_rank.data_ptr(),
+            self.item_row.data_ptr(), self.status.data_ptr(), self._s()), "sb_ep_exchange_dispatch")
+        self.launches += 1
+
+    def stage_experts_and_shared(self) -> None:
+        """Routed groups and the shared expert in one pair of weight-streaming launches."""
+        w, b, t = self.w, self.bufs, self._t
+        has_shared = bool(w.shared_inter) and t > 0
+        check(lib.sb_grouped_swiglu_mixed(
+            b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
+            w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
+            self.hbuf.data_ptr(), b.local["y"], self.ep * _lib.DECODE_MAX_TOKENS,
+            self._x.data_ptr() if has_shared else None,
+            w.shared_w13.data_ptr() if has_shared else None, w.shared_w2.data_ptr() if has_shared else None,
+            self.shared_scale.data_ptr() if has_shared and w.shared_gate_w is not None else None,
+            w.shared_inter if has_shared else 0, t if has_shared else 0,
+            self.shared_h.data_ptr() if has_shared else None, self.shared_out.data_ptr() if has_shared else None,
+            self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed")
+        self.launches += 2
 
     def stage_plan(self) -> None:
         check(lib.sb_ep_plan(self.bufs.local["ctl"], self.owner.data_ptr(), self.w.num_experts,
@@ -255,6 +318,15 @@ class EpRank:
         w, t = self.w, self._t
         if not w.shared_inter or t == 0:
             return
+        if self._small():
+            check(lib.sb_decode_experts(
+                self._x.data_ptr(), None, 1, None, None, None, None, None, w.hidden, w.inter, 1, None, None,
+                w.shared_w13.data_ptr(), w.shared_w2.data_ptr(),
+                self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, w.shared_inter, t,
+                self.shared_h.data_ptr(), self.shared_out.data_ptr(), self.status.data_ptr(), self._s()),
+                "sb_decode_experts(shared)")
+            self.launches += 2
+            return
         check(lib.sb_grouped_swiglu(
             self._x.data_ptr(), None, t, w.shared_w13.data_ptr(), w.shared_w2.data_ptr(), None,
             self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, t, w.hidden,
@@ -264,6 +336,15 @@ class EpRank:
 
     def stage_experts(self) -> None:
         w, b = self.w, self.bufs
+        if self._small():
+            # few rows per expert arrive in a decode step, whatever the peers sent
+            check(lib.sb_grouped_swiglu_mixed(
+                b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
+                w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
+                self.hbuf.data_ptr(), b.local["y"], 0, None, None, None, None, 0, 0, None, None,
+                self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed(routed)")
+            self.launches += 4
+            return
         check(lib.sb_grouped_swiglu(
             b.local["rows"], self.recv_tiles.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
             w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
@@ -300,7 +381,6 @@ class ExpertParallelLayer:
                 bufs = PeerBuffers(weights.hidden, weights.num_experts, cap, ep, rank)
                 bufs.allocate_local()
                 exchange_handles(bufs, process_group)
-            bufs.epoch = 0
             self._shared_bufs[key] = bufs
         self.bufs = bufs
         self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits)
@@ -324,8 +404,7 @@ class ExpertParallelLayer:
         return self.r.topk_w
 
     def _barrier(self) -> None:
-        self.bufs.epoch += 1
-        self.r.stage_barrier(self.bufs.epoch)
+        self.r.stage_barrier()
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         r = self.r
@@ -355,6 +434,20 @@ class ExpertParallelLayer:
                 mark("shared_swiglu")
                 self._barrier()
                 mark("barrier(rows landed)")
+            elif x.shape[0] <= _lib.DECODE_MAX_TOKENS and r.small_batch_kernels:
+                # Decode-sized step: launch-bound, so one stream, the fewest
+                # launches, nothing that a CUDA graph capture could not record.
+                # Every rank of the group must take this branch in the same step
+                # (the fused kernel runs two barriers): callers keep decode
+                # batches within DECODE_MAX_TOKENS rows on all ranks, or set
+                # small_batch_kernels = False everywhere.
+                r.stage_route(x)
+                r.stage_exchange_dispatch()
+                r.stage_experts_and_shared()
+                self._barrier()
+                res = r.stage_combine(out)
+                self.last_launches = r.launches
+                return res
             else:
                 # The shared expert needs nothing from the peers: it runs on the
                 # caller's stream while count exchange, plan, dispatch and the

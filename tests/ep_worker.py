@@ -34,6 +34,35 @@ def main():
             idx, _ = blk.topk(tokens)
             assert torch.equal(idx, want_idx), "indices differ on rank %d" % rank
             assert torch.equal(out, want), "EP rows differ from the single-GPU layer on rank %d" % rank
+        # decode-sized steps (fused count exchange + plan, weight-streaming expert
+        # kernels), eagerly and replayed from a captured CUDA graph
+        t_small = 8 if rank % 2 == 0 else 5
+        ref_small = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, 16)
+        xs = [synth.make_hidden(t_small, shape.hidden, seed=700 + 10 * it + rank).to(torch.bfloat16).to(dev)
+              for it in range(3)]
+        wants = [ref_small.forward(x)[0].clone() for x in xs]
+        for it in range(3):
+            out = blk.forward_device(xs[it]).clone()
+            torch.cuda.synchronize()
+            blk.check_status()
+            assert torch.equal(out, wants[it]), "decode-sized EP rows differ on rank %d" % rank
+        dist.barrier()
+        x_static = xs[0].clone()
+        out_static = torch.empty_like(x_static)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            blk.forward_device(x_static, out_static)
+            with torch.cuda.graph(graph, stream=side):
+                blk.forward_device(x_static, out_static)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        for it in range(3):
+            x_static.copy_(xs[it])
+            graph.replay()
+            torch.cuda.synchronize()
+            blk.check_status()
+            assert torch.equal(out_static, wants[it]), "graph-replayed EP rows differ on rank %d" % rank
         dist.barrier()
     print("EP_WORKER_OK rank %d" % rank, flush=True)
     dist.barrier()

@@ -37,9 +37,11 @@ def _rank_weights(w, rank, ep, dev):
     return lw
 
 
-@pytest.mark.parametrize("shape_name,ep,tokens", [("TINY", 2, [70, 33]), ("TINY", 4, [5, 0, 130, 64]),
-                                                  ("QWEN_MOE", 2, [300, 212])])
-def test_simulated_ranks_match_single_gpu(shape_name, ep, tokens):
+@pytest.mark.parametrize("shape_name,ep,tokens,small", [
+    ("TINY", 2, [70, 33], False), ("TINY", 4, [5, 0, 130, 64], False), ("QWEN_MOE", 2, [300, 212], False),
+    # decode-sized batches: the per-row router, single-CTA sort and weight-streaming expert kernels
+    ("TINY", 4, [8, 3, 16, 1], True), ("QWEN_MOE", 2, [8, 8], True), ("QWEN_MOE", 4, [16, 1, 0, 7], True)])
+def test_simulated_ranks_match_single_gpu(shape_name, ep, tokens, small):
     from sparse_b200.ep import EpRank, PeerBuffers, recv_capacity
     from sparse_b200.layer import LayerRunner, LayerWeights
     dev = torch.device("cuda:0")
@@ -56,6 +58,8 @@ def test_simulated_ranks_match_single_gpu(shape_name, ep, tokens):
     owner = [e % ep for e in range(shape.num_experts)]
     ranks = [EpRank(_rank_weights(w, r, ep, dev), shape.top_k, max(max_t, 1), r, ep, owner, bufs[r])
              for r in range(ep)]
+    for rk in ranks:
+        rk.small_batch_kernels = small      # off: every rank uses the kernels of the single-GPU run below
     x_all = synth.make_hidden(sum(tokens), shape.hidden, seed=5).to(torch.bfloat16)
     xs = [t.contiguous().to(dev) for t in torch.split(x_all, tokens)]
     try:
@@ -82,7 +86,11 @@ def test_simulated_ranks_match_single_gpu(shape_name, ep, tokens):
         got = torch.cat(outs)
         got_idx = torch.cat([ranks[r].topk_idx[:tokens[r]] for r in range(ep)])
         assert torch.equal(got_idx, ref_idx)
-        assert torch.equal(got, ref_out), "a row's result must not depend on where it was computed"
+        if small:       # different GEMM kernels than the single-GPU run: same values up to summation order
+            assert rel_l2(got.cpu(), ref_out.cpu()) < 5e-3
+            assert float((got.float() - ref_out.float()).abs().max()) < 2e-2
+        else:
+            assert torch.equal(got, ref_out), "a row's result must not depend on where it was computed"
         # and the oracle
         res = mo.moe_block_forward(x_all, mo.cast_weights(w, torch.bfloat16), shape.top_k)
         assert torch.equal(got_idx.cpu().long(), res["topi"])
