@@ -281,6 +281,55 @@ def token_sweep(lw, shape, peaks, counts=(1, 8, 64, 256, 1024)):
     return out
 
 
+def decode_stack(lw, shape, peaks, layers=24, counts=(1, 8, 16)):
+    """A decode step through a 24-layer stack of MoE blocks, each layer with its
+    own 1.1 GB of weights (so nothing survives in L2 from layer to layer), the
+    output of a layer plus its input feeding the next, captured as ONE CUDA graph
+    and replayed: what the MoE layers cost inside a graph-captured decode loop of
+    a 24-layer model (attention not included)."""
+    from sparse_b200.layer import LayerRunner
+    from sparse_b200 import synth
+    dev = lw.device
+    stack = [lw] + [lw.clone() for _ in range(layers - 1)]
+    out = {}
+    for t in counts:
+        runners = [LayerRunner(w_l, shape.top_k, t) for w_l in stack]
+        x0 = synth.make_hidden(t, shape.hidden, seed=77).to(torch.bfloat16).to(dev)
+        bufs = [torch.empty_like(x0) for _ in range(layers + 1)]
+        outs = [torch.empty_like(x0) for _ in range(layers)]
+
+        def step():
+            bufs[0].copy_(x0)
+            for li, r in enumerate(runners):
+                r.forward(bufs[li], outs[li])
+                torch.add(bufs[li], outs[li], out=bufs[li + 1])     # residual stream
+
+        step()
+        torch.cuda.synchronize()
+        touched = sum(int(torch.unique(r.topk_idx[:t]).numel()) for r in runners)
+        cap = torch.cuda.Stream(device=dev)
+        cap.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap):
+            step()
+            with torch.cuda.graph(graph, stream=cap):
+                step()
+        torch.cuda.current_stream(dev).wait_stream(cap)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        reps = 20
+        ms = _time_region(lambda i: graph.replay(), reps, torch.cuda.current_stream(dev)) / reps
+        for r in runners:
+            r.check_status()
+        hbm = touched * shape.routed_expert_bytes_bf16 + layers * 3 * shape.hidden * shape.shared_inter * 2
+        floor_ms = hbm / (peaks["hbm_gbs"] * 1e9) * 1e3
+        out[str(t)] = {"ms_per_step": ms, "tokens_per_s": t / (ms * 1e-3), "layers": layers,
+                       "us_per_layer": ms * 1e3 / layers, "experts_touched": touched,
+                       "hbm_floor_ms": floor_ms, "frac": floor_ms / ms}
+    return out
+
+
 def run_ours(args):
     from sparse_b200 import synth
     from sparse_b200.block import B200MoeBlock
@@ -480,7 +529,7 @@ def run_ours(args):
             stage_bytes = {}
             stage_flops = {"routed_swiglu": 2 * n_recv * h * 2 * i + 2 * n_recv * i * h,
                            "shared_swiglu": 2 * t * h * 2 * ish + 2 * t * ish * h}
-            distinct = len([e for e in range(shape.num_experts) if e % world == rank])
+            distinct = block.weights.n_slots          # experts this rank holds (replicas included)
         for name, ms in stage_ms.items():
             ent = {"ms": ms}
             if name in stage_bytes:
@@ -519,6 +568,7 @@ def run_ours(args):
             line["decode"] = decode
         if world == 1 and not args.no_sweep:
             line["sweep"] = token_sweep(block.weights, shape, peaks)
+            line["decode_stack"] = decode_stack(block.weights, shape, peaks)
         if world == 1 and not args.no_cpu_baseline:
             tps, ms, cores = cpu_reference_tokens_per_s(3, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",

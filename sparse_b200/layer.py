@@ -80,6 +80,15 @@ class LayerWeights:
     def set_slot_map(self, slot_of_expert: Sequence[int]) -> None:
         self.slot_of_expert.copy_(torch.tensor(list(slot_of_expert), dtype=torch.int32))
 
+    def clone(self) -> "LayerWeights":
+        """A second layer with its own copies of every device tensor."""
+        import copy
+        other = copy.copy(self)
+        for name, value in vars(self).items():
+            if isinstance(value, torch.Tensor):
+                setattr(other, name, value.clone())
+        return other
+
     @classmethod
     def from_block_weights(cls, w, device: torch.device) -> "LayerWeights":
         """All experts resident, slot = expert id.  `w` is a `synth.BlockWeights`."""
