@@ -66,6 +66,21 @@ static bool overlap_sort() {
   return v;
 }
 
+static int env_int(const char *name, int fallback) {
+  const char *e = getenv(name);
+  return (e && *e) ? atoi(e) : fallback;
+}
+// Largest batch for which the shared and the routed GEMM share the SMs by grid
+// size, and how many CTA pairs the shared expert gets then.
+static int split_tokens() {
+  static const int v = env_int("SPARSE_B200_SPLIT_TOKENS", 1024);
+  return v;
+}
+static int shared_pairs() {
+  static const int v = env_int("SPARSE_B200_SHARED_PAIRS", 16);
+  return v;
+}
+
 static int hybrid_rows() {
   static const int v = [] {
     const char *e = getenv("SPARSE_B200_HYBRID");
@@ -83,14 +98,14 @@ static int hybrid_rows() {
 int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, int dense_rows,
                                   const void *w13, const void *w2, const int32_t *slot_of_expert,
                                   const void *row_scale, int R_cap, int H, int I, int S, void *hbuf,
-                                  void *out, int32_t *status, cudaStream_t stream) {
+                                  void *out, int32_t *status, cudaStream_t stream, int max_pairs = 0) {
   if (!sb_w13_interleaved())
     return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
                                  H, I, S, hbuf, out, status, stream);
   const int light = (tile_table != nullptr && H % 32 == 0 && I % 32 == 0) ? hybrid_rows() : 0;
   if (light == 0)
     return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
-                                      R_cap, H, I, S, hbuf, out, status, 0, stream);
+                                      R_cap, H, I, S, hbuf, out, status, 0, max_pairs, stream);
   std::lock_guard<std::recursive_mutex> lock(g_side_mu);
   SideLane *lane = side_lane();
   if (lane == nullptr) return fail(SB_E_CUDA, "sb_grouped_swiglu: cannot create the side stream");
@@ -105,7 +120,7 @@ int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, i
   int32_t rc2 = SB_OK;
   if (rc == SB_OK)
     rc2 = launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
-                                     H, I, S, hbuf, out, status, light, stream);
+                                     H, I, S, hbuf, out, status, light, 0, stream);
   SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
   return rc != SB_OK ? rc : rc2;
 }
@@ -255,7 +270,7 @@ int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, con
                                      status, 2, limit, shared_x, st);
   if (rc != SB_OK || max_group_rows > 0) return rc;     // the caller's bound says no group is left over
   return launch_grouped_swiglu_pair(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S,
-                                    hbuf, out, status, limit, st);
+                                    hbuf, out, status, limit, 0, st);
 }
 
 int32_t sb_route_decode(const void *x, const void *w_router, const float *router_bias, const void *w_shared_gate,
@@ -345,39 +360,52 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                           L->out, stream);
   }
-  // The shared expert needs nothing from the sort: it runs on the caller's
-  // stream while count/scan/scatter/gather (one busy SM, then a short copy) run
-  // beside it on the library's side stream; the routed GEMM waits for both.
+  // The shared expert needs nothing from the routing: it runs on the caller's
+  // stream while count/scan/scatter/gather run beside it on the library's side
+  // stream.  Up to split_tokens() rows, where both GEMMs stream weights and
+  // neither fills the machine, the routed GEMM follows on the side stream too
+  // and the two share the SMs by grid size (a few CTA pairs for the shared
+  // expert's few tiles, the rest for the routed groups); above that they run
+  // one after the other on all SMs.
   SideLane *lane = nullptr;
   std::unique_lock<std::recursive_mutex> lock(g_side_mu, std::defer_lock);
   if (Is > 0 && overlap_sort()) {
     lock.lock();
     lane = side_lane();
   }
-  cudaStream_t sort_stream = stream;
+  const int all_pairs = sb_device_sm_count() / 2;
+  const bool split = lane != nullptr && sb_w13_interleaved() && T <= split_tokens() && hybrid_rows() == 0 &&
+                     all_pairs > 2 * shared_pairs();
+  cudaStream_t side = stream;
   if (lane != nullptr) {
     SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
     SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
-    sort_stream = lane->stream;
+    side = lane->stream;
   }
   rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes,
                       s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
-                      s.tile_table, sort_stream);
+                      s.tile_table, side);
+  if (rc == SB_OK && split)
+    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
+                                   s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, side,
+                                   all_pairs - shared_pairs());
   if (lane != nullptr) SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
   int32_t rc_shared = SB_OK;
   if (rc == SB_OK && Is > 0)
     rc_shared = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
                                           L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
-                                          s.shared_out, status, stream);
+                                          s.shared_out, status, stream, split ? shared_pairs() : 0);
   if (lane != nullptr) {
     SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
     lock.unlock();
   }
   if (rc != SB_OK) return rc;
   if (rc_shared != SB_OK) return rc_shared;
-  rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
-                                 s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
-  if (rc != SB_OK) return rc;
+  if (!split) {
+    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
+                                   s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
+    if (rc != SB_OK) return rc;
+  }
   return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                         L->out, stream);
 }

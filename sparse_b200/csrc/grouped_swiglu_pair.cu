@@ -12,7 +12,8 @@
 //    (32 KB instead of 48 KB per CTA for the same flops), the tensor cores read
 //    the token half of the peer through distributed shared memory.  That cuts
 //    L2->SM traffic by a third, which is what capped the single-CTA kernel.
-//  * six 32 KB stages; TMEM holds two 128-lane x 256-column accumulators per CTA.
+//  * six 36 KB stages (one K step of a full tile, or two K steps of a tile of
+//    at most 32 tokens); TMEM holds two 128-lane x 256-column accumulators per CTA.
 //  * pass 1 reads the gate/up slab with gate and up rows interleaved
 //    (row 2j = gate_j, row 2j+1 = up_j), so the two values a SwiGLU output
 //    needs sit in adjacent TMEM lanes = adjacent threads: one shuffle, no
@@ -27,6 +28,7 @@
 // All mbarrier waits are bounded (2 s); on expiry the CTA sets an abort flag,
 // reports through `status`, drains, joins the cluster barrier, frees TMEM.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -45,7 +47,12 @@ constexpr int kThreads = 320;         // producer warp, MMA warp, 8 epilogue war
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = kRowsPerCta * kBlockK * 2;      // 16 KB
 constexpr uint32_t kBBytes = (kMaxN / 2) * kBlockK * 2;      // 16 KB (this CTA's half of the tokens)
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kLightTokBytes = 16 * kBlockK * 2;         // 2 KB: a 16-row token box of one K step
+// A stage holds one K step of a full tile (A 16 KB + B up to 16 KB) or, for a
+// light tile (at most 16 tokens per CTA), TWO K steps (A, A', then the two
+// 2 KB token boxes): half as many barrier round trips per weight byte, twice
+// the bytes in flight, which is what bounds a tile that is pure weight traffic.
+constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kLightTokBytes;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + 256;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
@@ -169,12 +176,13 @@ __device__ __forceinline__ uint32_t idesc_m256(int n) {
 struct Chunk { int slot, tok_begin, tok_end; };
 
 __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense_rows,
-                                            const int32_t *slot_of_expert, int c, int skip_rows_upto) {
+                                            const int32_t *slot_of_expert, int c, int skip_rows_upto,
+                                            int dense_chunk) {
   Chunk t;
   if (tile_table == nullptr) {
     t.slot = 0;
-    t.tok_begin = c * kMaxN;
-    t.tok_end = min(dense_rows, t.tok_begin + kMaxN);
+    t.tok_begin = c * dense_chunk;
+    t.tok_end = min(dense_rows, t.tok_begin + dense_chunk);
   } else {
     const int4 e = __ldg(reinterpret_cast<const int4 *>(tile_table + kTileHeaderInts) + c);
     t.slot = slot_of_expert ? __ldg(slot_of_expert + e.x) : e.x;
@@ -192,7 +200,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                  const int32_t *__restrict__ tile_table, int dense_rows,
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
-                 int32_t *__restrict__ status, int skip_rows_upto) {
+                 int32_t *__restrict__ status, int skip_rows_upto, int dense_chunk, int light_max) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -207,7 +215,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const uint32_t cta = cluster_ctarank();               // 0 = leader
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
-  const int n_chunks = tile_table ? __ldg(tile_table) : (dense_rows + kMaxN - 1) / kMaxN;
+  const int n_chunks = tile_table ? __ldg(tile_table) : (dense_rows + dense_chunk - 1) / dense_chunk;
   const int total = n_chunks * n_wtiles;
 
   if (threadIdx.x == 0) {
@@ -235,7 +243,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       bool ok = true;
       for (int tile = pair; ok && tile < total; tile += n_pairs) {
         const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto);
+        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk);
         if (ch.slot == kSlotSkip) continue;
         if (ch.slot < 0 || ch.slot >= n_slots) {
           if (status) atomicExch(status, 2);
@@ -249,13 +257,18 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int half = n >> 1;
         const CUtensorMap *tok_map = half <= 16 ? &tm_x16 : (half <= 64 ? &tm_x64 : &tm_x);
         const uint32_t tok_bytes = (half <= 16 ? 16u : (half <= 64 ? 64u : 128u)) * kBlockK * 2;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const bool light = half <= light_max;
+        for (int kb = 0; kb < num_kb; kb += light ? 2 : 1) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
           const uint32_t sa = smem_base + stage * kStageBytes;
-          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * (kABytes + tok_bytes));
-          tma_pair_load_3d(sa, &tm_w, full_leader, kb * kBlockK, wrow, ch.slot);
-          tma_pair_load_2d(sa + kABytes, tok_map, full_leader, kb * kBlockK, tok0);
+          const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
+          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * steps * (kABytes + tok_bytes));
+          for (int j = 0; j < steps; ++j)
+            tma_pair_load_3d(sa + j * kABytes, &tm_w, full_leader, (kb + j) * kBlockK, wrow, ch.slot);
+          for (int j = 0; j < steps; ++j)
+            tma_pair_load_2d(light ? sa + 2 * kABytes + j * kLightTokBytes : sa + kABytes, tok_map, full_leader,
+                             (kb + j) * kBlockK, tok0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -267,23 +280,27 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < total; tile += n_pairs) {
-        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles, skip_rows_upto);
+        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles, skip_rows_upto, dense_chunk);
         if (ch.slot == kSlotSkip) continue;
         const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
         const uint32_t idesc = idesc_m256(n);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * kMaxN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const bool light = (n >> 1) <= light_max;
+        for (int kb = 0; kb < num_kb; kb += light ? 2 : 1) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes;
-          const uint64_t adesc = umma_desc_sw128(sa);
-          const uint64_t bdesc = umma_desc_sw128(sa + kABytes);
+          const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
+          for (int j = 0; j < steps; ++j) {
+            const uint64_t adesc = umma_desc_sw128(sa + j * kABytes);
+            const uint64_t bdesc = umma_desc_sw128(light ? sa + 2 * kABytes + j * kLightTokBytes : sa + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k)
-            tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                             (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                               (kb | j | k) != 0 ? 1u : 0u);
+          }
           tc_commit_pair(bar_empty + 8 * stage);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -304,7 +321,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     int acc = 0; uint32_t acc_phase = 0;
     for (int tile = pair; tile < total; tile += n_pairs) {
       const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto);
+      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk);
       if (ch.slot == kSlotSkip) continue;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
       tc_fence_after();
@@ -420,6 +437,11 @@ template <int MODE>
 int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
                     int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto, cudaStream_t stream) {
+  // Dense rows are cut into chunks of kMaxN tokens.  (Smaller chunks give more
+  // tiles for a small batch but were slower on B200: every chunk re-streams the
+  // whole weight tile from L2.)
+  const int dense_chunk = kMaxN;
+  const int probe_light = 16;
   auto kern = pair_gemm_kernel<MODE>;
   SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
   // ask for the largest shared-memory split so that small kernels of other
@@ -430,7 +452,7 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
                                               slot_of_expert,
                                               static_cast<const __nv_bfloat16 *>(row_scale),
                                               static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
-                                              status, skip_rows_upto);
+                                              status, skip_rows_upto, dense_chunk, probe_light);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -439,11 +461,12 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
 
 // w13 must be in the INTERLEAVED row order (row 2j = gate_j, row 2j+1 = up_j);
 // tile_table must have been built with 256-row tiles.  Tile entries of at most
-// `skip_rows_upto` rows are left to the caller (0 = none).
+// `skip_rows_upto` rows are left to the caller (0 = none); `max_pairs` > 0
+// limits the grid to that many CTA pairs.
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
-                                   int skip_rows_upto, cudaStream_t stream) {
+                                   int skip_rows_upto, int max_pairs, cudaStream_t stream) {
   if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
     return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
   if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
@@ -462,8 +485,9 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   }
   if ((rc = make_map(&tm_w13, w13, (uint64_t)H, (uint64_t)2 * I, (uint64_t)S, "w13")) != SB_OK) return rc;
   if ((rc = make_map(&tm_w2, w2, (uint64_t)I, (uint64_t)H, (uint64_t)S, "w2")) != SB_OK) return rc;
-  const int grid = (sb_device_sm_count() / 2) * 2;
+  int grid = (sb_device_sm_count() / 2) * 2;
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
+  if (max_pairs > 0 && 2 * max_pairs < grid) grid = 2 * max_pairs;     // leave the other SMs to a concurrent launch
   rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
                                 H / kBlockK, S, status, grid, skip_rows_upto, stream);
   if (rc != SB_OK) return rc;
