@@ -349,14 +349,6 @@ int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, i
                    int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
                    int32_t *tile_table, void *stream);
 
-/* sb_ep_publish_counts + sb_ep_barrier_seq + sb_ep_plan as ONE single-CTA
- * launch, for decode-sized steps where launches dominate (replaces the count
- * all-to-all and host sync of utils/eval_core.py:14883-14911). */
-int32_t sb_ep_exchange_plan(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
-                            uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank, int32_t ep,
-                            int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets, int32_t *tile_table,
-                            int32_t *status, void *stream);
-
 /* The whole send side of a decode-sized step as ONE single-CTA launch:
  * sb_ep_publish_counts, barrier, sb_ep_plan, sb_ep_dispatch, barrier ("every
  * rank's rows have landed"); arguments as in those calls, `owner` the full

@@ -71,7 +71,6 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_publish_counts": (i32, [vp, i32, i32, i32, C.POINTER(vp), vp]),
     "sb_ep_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, vp, vp]),
     "sb_ep_barrier_seq": (i32, [C.POINTER(vp), i32, i32, vp, vp, vp]),
-    "sb_ep_exchange_plan": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
     "sb_ep_exchange_dispatch": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp,
                                       vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp, vp, vp]),
     "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),

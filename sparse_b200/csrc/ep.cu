@@ -180,25 +180,6 @@ ep_plan_kernel(const int32_t *__restrict__ counts_all, const int32_t *__restrict
   plan_body(counts_all, owner, E, rank, ep, tile_cap, tile_rows, dst_base, recv_offsets, tile_table, plan_smem);
 }
 
-// publish + barrier + plan in one single-CTA launch (the decode-sized step is
-// launch-bound): counts go out to every peer, the barrier makes all rows of the
-// local counts matrix valid, the plan is derived from it.
-__global__ void __launch_bounds__(256)
-ep_exchange_plan_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs counts_all, PeerPtrs flags,
-                        uint32_t *epoch_counter, const int32_t *__restrict__ owner, int E, int rank, int ep,
-                        int tile_cap, int tile_rows, int32_t *__restrict__ dst_base,
-                        int32_t *__restrict__ recv_offsets, int32_t *__restrict__ tile_table,
-                        int32_t *__restrict__ status) {
-  extern __shared__ int plan_smem[];
-  publish_body(local_offsets, E, rank, ep, counts_all);
-  __threadfence_system();
-  const uint32_t epoch = next_epoch(epoch_counter);      // its __syncthreads also orders the stores above
-  barrier_body(flags, rank, ep, epoch, status);
-  __syncthreads();
-  plan_body(static_cast<const int32_t *>(counts_all.p[rank]), owner, E, rank, ep, tile_cap, tile_rows, dst_base,
-            recv_offsets, tile_table, plan_smem);
-}
-
 // One warp per item: activation row and route weight to the owner's buffer.
 __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const int32_t *__restrict__ item_expert,
                                               const __nv_bfloat16 *__restrict__ item_scale,
@@ -422,29 +403,6 @@ int32_t sb_ep_barrier_seq(void *const *peer_flags, int32_t rank, int32_t ep, uin
   int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier_seq");
   if (rc != SB_OK) return rc;
   ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, 0u, epoch_counter, status);
-  SB_LAUNCH_CHECK();
-  return SB_OK;
-}
-
-int32_t sb_ep_exchange_plan(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
-                            uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank, int32_t ep,
-                            int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets, int32_t *tile_table,
-                            int32_t *status, void *stream) {
-  if (!local_offsets || !epoch_counter || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 ||
-      E > kMaxExperts || rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
-    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_plan: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
-  PeerPtrs pc, pf;
-  int32_t rc = fill_peers(&pc, peer_counts, ep, "sb_ep_exchange_plan");
-  if (rc != SB_OK) return rc;
-  if ((rc = fill_peers(&pf, peer_flags, ep, "sb_ep_exchange_plan")) != SB_OK) return rc;
-  const int tile_cap = recv_cap / SB_TILE_M + E;
-  const size_t smem = ((size_t)2 * ep * E + 2 * (size_t)(E + 1)) * sizeof(int);
-  if (smem > 48 * 1024)
-    SB_CUDA_CHECK(cudaFuncSetAttribute(ep_exchange_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
-  ep_exchange_plan_kernel<<<1, 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      local_offsets, pc, pf, epoch_counter, owner, E, rank, ep, tile_cap, sb_tile_rows(), dst_base,
-      recv_offsets, tile_table, status);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -259,16 +259,6 @@ class EpRank:
               "sb_ep_barrier_seq")
         self.launches += 1
 
-    def stage_exchange_plan(self) -> None:
-        """publish + barrier + plan as one launch."""
-        b = self.bufs
-        check(lib.sb_ep_exchange_plan(
-            self.local_offsets.data_ptr(), b.ptr_array("ctl"), b.ptr_array("ctl", b.flags_offset),
-            b.local["ctl"] + b.epoch_offset, self.owner.data_ptr(), self.w.num_experts, self.rank, self.ep,
-            b.recv_cap, self.dst_base.data_ptr(), self.recv_offsets.data_ptr(), self.recv_tiles.data_ptr(),
-            self.status.data_ptr(), self._s()), "sb_ep_exchange_plan")
-        self.launches += 1
-
     def stage_exchange_dispatch(self) -> None:
         """publish + barrier + plan + dispatch + barrier as one launch (decode-sized steps)."""
         b, w, t, k = self.bufs, self.w, self._t, self.top_k

@@ -221,6 +221,119 @@ def test_grouped_swiglu_against_oracle(h, i, e, counts):
     assert float((got_h == want_h).float().mean()) > 0.9
 
 
+@pytest.mark.parametrize("bound", [0, 64])
+def test_mixed_swiglu_few_rows_per_expert(bound):
+    """sb_grouped_swiglu_mixed (weight-streaming kernels, groups swept 16 rows at a
+    time, optional shared expert in the same launches) against the oracle: groups
+    of 1..40 rows, with the caller's row bound (no tile kernel launched) and
+    without it (groups above 16 rows go to the tile kernel)."""
+    from sparse_b200 import ops, _lib
+    torch.manual_seed(21 + bound)
+    bf = torch.bfloat16
+    h, i, ish, e = 256, 192, 320, 6
+    counts = [1, 0, 16, 17, 40, 5]
+    gate = [(torch.randn(i, h) * 0.05).to(bf) for _ in range(e)]
+    up = [(torch.randn(i, h) * 0.05).to(bf) for _ in range(e)]
+    down = [(torch.randn(h, i) * 0.05).to(bf) for _ in range(e)]
+    sg, su, sd = [(torch.randn(*s) * 0.05).to(bf) for s in ((ish, h), (ish, h), (h, ish))]
+    ids = torch.cat([torch.full((c,), ee, dtype=torch.int32) for ee, c in enumerate(counts)])
+    n = ids.numel()
+    x = torch.randn(n, h).to(bf)
+    scale = torch.rand(n).to(bf)
+    t_sh = 23
+    x_sh = torch.randn(t_sh, h).to(bf)
+    sh_scale = torch.rand(t_sh).to(bf)
+    d = dev()
+    p = ops.permute(x.to(d), ids.to(d), e, 1, item_scale=scale.to(d))
+    w13 = torch.stack([pack_w13(gate[ee], up[ee]) for ee in range(e)]).to(d)
+    w2 = torch.stack(down).to(d)
+    sw13 = pack_w13(sg, su).unsqueeze(0).to(d)
+    sw2 = sd.unsqueeze(0).to(d)
+    r_cap = p.rows.shape[0]
+    hbuf = torch.zeros((r_cap, i), dtype=bf, device=d)
+    out = torch.zeros((r_cap, h), dtype=bf, device=d)
+    sh_h = torch.zeros((t_sh, ish), dtype=bf, device=d)
+    sh_out = torch.zeros((t_sh, h), dtype=bf, device=d)
+    xs_d, shs_d = x_sh.to(d), sh_scale.to(d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    with torch.cuda.device(d):
+        _lib.check(_lib.lib.sb_grouped_swiglu_mixed(
+            p.rows.data_ptr(), p.tile_table.data_ptr(), w13.data_ptr(), w2.data_ptr(), None,
+            p.slot_scale.data_ptr(), r_cap, h, i, e, hbuf.data_ptr(), out.data_ptr(), bound,
+            xs_d.data_ptr(), sw13.data_ptr(), sw2.data_ptr(), shs_d.data_ptr(), ish, t_sh,
+            sh_h.data_ptr(), sh_out.data_ptr(), status.data_ptr(),
+            torch.cuda.current_stream(d).cuda_stream), "sb_grouped_swiglu_mixed")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want, _ = _oracle_grouped(x, p.expert_offsets.cpu(), gate, up, down, scale)
+    got = out.cpu()[:n]
+    assert rel_l2(got, want) < REL_L2
+    assert float((got.float() - want.float()).abs().max()) < MAX_ABS
+    want_sh = (mo.expert_mlp(x_sh, sg, su, sd).float() * sh_scale.float()[:, None]).to(bf)
+    assert rel_l2(sh_out.cpu(), want_sh) < REL_L2
+    assert float((sh_out.cpu().float() - want_sh.float()).abs().max()) < MAX_ABS
+
+
+def test_route_decode_equals_router_plus_sort():
+    """sb_route_decode (two launches) gives the bits of sb_router_topk + sb_permute."""
+    from sparse_b200 import ops, _lib
+    shape = synth.QWEN_MOE
+    w = block_weights("QWEN_MOE", 1.2)
+    d = dev()
+    for t in (1, 7, 16):
+        x = synth.make_hidden(t, shape.hidden, seed=40 + t).to(torch.bfloat16).to(d)
+        rw = w.router.to(torch.bfloat16).to(d)
+        rb = w.router_bias.to(torch.bfloat16).float().to(d)
+        sgw = w.sh_scalar_gate.reshape(-1).to(torch.bfloat16).to(d)
+        idx, wts, logits, sg = ops.router_topk(x, rw, shape.top_k, bias=rb, w_shared_gate=sgw)
+        p = ops.permute(x, idx.reshape(-1), shape.num_experts, shape.top_k, item_scale=wts.reshape(-1))
+        e, k = shape.num_experts, shape.top_k
+        i32, bf = torch.int32, torch.bfloat16
+        ws = torch.empty(16 * e, dtype=torch.float32, device=d)
+        idx2 = torch.empty((t, k), dtype=i32, device=d)
+        w2 = torch.empty((t, k), dtype=bf, device=d)
+        lg2 = torch.empty((t, e), dtype=bf, device=d)
+        sg2 = torch.empty((t,), dtype=bf, device=d)
+        offs = torch.empty(e + 1, dtype=i32, device=d)
+        soi = torch.empty(t * k, dtype=i32, device=d)
+        ios = torch.empty(t * k, dtype=i32, device=d)
+        ssc = torch.empty(max(t * k, 128), dtype=bf, device=d)
+        tiles = torch.empty(_lib.lib.sb_tile_table_ints(t * k, e), dtype=i32, device=d)
+        with torch.cuda.device(d):
+            _lib.check(_lib.lib.sb_route_decode(
+                x.data_ptr(), rw.data_ptr(), rb.data_ptr(), sgw.data_ptr(), t, shape.hidden, e, k, 0, 0,
+                ws.data_ptr(), idx2.data_ptr(), w2.data_ptr(), lg2.data_ptr(), sg2.data_ptr(), offs.data_ptr(),
+                soi.data_ptr(), ios.data_ptr(), ssc.data_ptr(), tiles.data_ptr(),
+                torch.cuda.current_stream(d).cuda_stream), "sb_route_decode")
+        torch.cuda.synchronize()
+        assert torch.equal(idx2, idx) and torch.equal(w2, wts) and torch.equal(lg2, logits) and torch.equal(sg2, sg)
+        assert torch.equal(offs, p.expert_offsets) and torch.equal(soi, p.slot_of_item)
+        assert torch.equal(ios, p.item_of_slot[:t * k]) and torch.equal(ssc[:t * k], p.slot_scale[:t * k])
+        n_tiles = int(p.tile_table[0].item())
+        assert torch.equal(tiles[:4 + 4 * n_tiles], p.tile_table[:4 + 4 * n_tiles])
+
+
+def test_host_pipeline_matches_device_forward():
+    from sparse_b200.block import B200MoeBlock
+    shape = synth.TINY
+    w = block_weights("TINY", 1.2)
+    blk = B200MoeBlock.from_block_weights(w, dev(), max_tokens=200)
+    pipe = blk.host_pipeline(depth=2)
+    xs = [synth.make_hidden(t, shape.hidden, seed=60 + j).to(torch.bfloat16).pin_memory()
+          for j, t in enumerate((200, 33, 1, 200, 150))]
+    outs = [torch.empty_like(x).pin_memory() for x in xs]
+    tickets = [pipe.submit(x, o) for x, o in zip(xs, outs)]
+    pipe.wait(tickets[-1])
+    pipe.drain()
+    for x, o in zip(xs, outs):
+        want = blk.forward_device(x.to(dev())).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(o.to(dev()), want)
+    with pytest.raises(ValueError):
+        pipe.wait(0)                      # no longer in flight
+    blk.check_status()
+
+
 def test_dense_swiglu_shared_expert_shape():
     from sparse_b200 import ops
     torch.manual_seed(9)
