@@ -29,6 +29,8 @@ combine_kernel(const uint4 *__restrict__ rows, const int32_t *__restrict__ slot_
                const int32_t *__restrict__ idx, const uint4 *__restrict__ shared_out, int T,
                int vec_per_row, int K, uint4 *__restrict__ out) {
   __shared__ int s_slot[kMaxK];
+  pdl_launch_dependents();
+  pdl_wait();
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
     if (threadIdx.x == 0) {
       // insertion sort of the K (expert id, slot) pairs, stable in slot order
@@ -73,9 +75,9 @@ int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const 
   int max_blocks = sb_device_sm_count() * 16;
   if (blocks > max_blocks) blocks = max_blocks;
   int threads = H / 8 >= 256 ? 256 : ((H / 8 + 31) / 32) * 32;
-  combine_kernel<<<blocks, threads, 0, stream>>>(
-      static_cast<const uint4 *>(rows_out), slot_of_item, idx,
-      static_cast<const uint4 *>(shared_out), T, H / 8, K, static_cast<uint4 *>(out));
+  SB_CUDA_CHECK(launch_pdl(combine_kernel, dim3(blocks), dim3(threads), 0, stream,
+                           static_cast<const uint4 *>(rows_out), slot_of_item, idx,
+                           static_cast<const uint4 *>(shared_out), T, H / 8, K, static_cast<uint4 *>(out)));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -25,6 +25,8 @@
 // directly when the rows are already expert-sorted (`item_of_slot` null).
 // Groups of more than 16 rows are left alone: next to the tile kernel this
 // pair of launches serves the light groups of a large batch.
+#include <stdlib.h>
+
 #include "sb_common.cuh"
 
 namespace sb {
@@ -122,6 +124,8 @@ decode_gate_up_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__rest
                       __nv_bfloat16 *__restrict__ shared_h, int ks_n, int max_rows,
                       int32_t *__restrict__ status) {
   __shared__ float red[kWarps][8][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int rg_n = kWarps / ks_n, rg = warp / ks_n, ks = warp % ks_n;
@@ -207,6 +211,8 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
                    int I_sh, int T, __nv_bfloat16 *__restrict__ shared_out, int ks_routed, int ks_shared,
                    int max_rows) {
   __shared__ float red[kWarps][8][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int n_groups = tile_table ? __ldg(tile_table) : 0;
@@ -302,8 +308,9 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
   const int sms = sb_device_sm_count();
   if (sms <= 0) return fail(SB_E_CUDA, "sb_decode_experts: no CUDA device");
   const int grid = sms * (ctas_per_sm == 1 ? 1 : 2);       // grid-stride over the block tasks
-  // K slices per row group: about 16-22 chunks of 32 elements per warp
-  auto slices = [](int k) { const int ch = k / 32; return ch > 96 ? 8 : ch > 48 ? 4 : ch > 24 ? 2 : 1; };
+  // K slices per row group (measured on B200: 2 slices for 64 chunks of 32
+  // elements, 1 for 44, 4 for 176 beat finer splits by up to 8 % at 8 tokens)
+  auto slices = [](int k) { const int ch = k / 32; return ch > 128 ? 4 : ch > 48 ? 2 : 1; };
   const int ks1 = slices(H), ks2_routed = slices(I), ks2_shared = slices(I_sh > 0 ? I_sh : I);
   // Next to the tile kernel (ctas_per_sm == 1) the SM must already be in the
   // large-shared-memory configuration that kernel needs, or the two could not
@@ -311,19 +318,21 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
   const int carveout = ctas_per_sm == 1 ? (int)cudaSharedmemCarveoutMaxShared : (int)cudaSharedmemCarveoutDefault;
   SB_CUDA_CHECK(cudaFuncSetAttribute(decode_gate_up_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, carveout));
   SB_CUDA_CHECK(cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, carveout));
-  decode_gate_up_kernel<<<grid, kThreads, 0, stream>>>(
+  SB_CUDA_CHECK(launch_pdl(
+      decode_gate_up_kernel, dim3(grid), dim3(kThreads), 0, stream,
       static_cast<const __nv_bfloat16 *>(x), item_of_slot, items_per_row, tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w13), H, I, n_slots, sb_w13_interleaved(),
       static_cast<__nv_bfloat16 *>(hbuf), static_cast<const __nv_bfloat16 *>(shared_x),
       static_cast<const __nv_bfloat16 *>(shared_w13), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_h), ks1, max_rows, status);
+      static_cast<__nv_bfloat16 *>(shared_h), ks1, max_rows, status));
   SB_LAUNCH_CHECK();
-  decode_down_kernel<<<grid, kThreads, 0, stream>>>(
+  SB_CUDA_CHECK(launch_pdl(
+      decode_down_kernel, dim3(grid), dim3(kThreads), 0, stream,
       static_cast<const __nv_bfloat16 *>(hbuf), tile_table, slot_of_expert,
       static_cast<const __nv_bfloat16 *>(w2), static_cast<const __nv_bfloat16 *>(row_scale), H, I, n_slots,
       static_cast<__nv_bfloat16 *>(y), static_cast<const __nv_bfloat16 *>(shared_h),
       static_cast<const __nv_bfloat16 *>(shared_w2), static_cast<const __nv_bfloat16 *>(shared_scale), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, max_rows);
+      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, max_rows));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -347,6 +347,8 @@ router_rows_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const fl
                    const IN *__restrict__ wsg, int T, int H, int E, int fp32_logits,
                    float *__restrict__ ws, void *__restrict__ out_logits, IN *__restrict__ out_shared) {
   constexpr int kVecPerGroup = sizeof(IN) == 2 ? 1 : 2;
+  pdl_launch_dependents();
+  pdl_wait();
   const int NR = E + (wsg != nullptr ? 1 : 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x;
@@ -480,6 +482,8 @@ route_sort_small_kernel(const float *__restrict__ logits, int T, int E, int K, i
   __shared__ float slog[16][kMaxExperts];
   __shared__ int s_exp[kSmallMaxItems];
   __shared__ int s_off[kMaxExperts + 1];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp < T) {
     for (int e = lane; e < E; e += 32) slog[warp][e] = logits[(size_t)warp * E + e];
@@ -545,19 +549,20 @@ int32_t launch_router_decode(const void *x, const void *wg, const float *bias, c
     return fail(SB_E_INVALID_ARG, "router (decode): bad arguments");
   const int NR = E + (wsg ? 1 : 0);
   dim3 grid(T, (NR + kRouterWarps - 1) / kRouterWarps);
-  router_rows_kernel<__nv_bfloat16><<<grid, kRouterThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(wg), bias,
-      static_cast<const __nv_bfloat16 *>(wsg), T, H, E, fp32_logits, ws, out_logits,
-      static_cast<__nv_bfloat16 *>(out_shared_scale));
+  SB_CUDA_CHECK(launch_pdl(router_rows_kernel<__nv_bfloat16>, grid, dim3(kRouterThreads), 0, stream,
+                           static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(wg), bias,
+                           static_cast<const __nv_bfloat16 *>(wsg), T, H, E, fp32_logits, ws, out_logits,
+                           static_cast<__nv_bfloat16 *>(out_shared_scale)));
   SB_LAUNCH_CHECK();
   if (tile_table != nullptr) {
     // softmax/top-k and the expert sort in one single-CTA launch
     if (T > 16 || !expert_offsets || !slot_of_item || !item_of_slot || !slot_scale)
       return fail(SB_E_INVALID_ARG, "router (decode): sort outputs need T <= 16 and all tables");
     const int warps = T > 4 ? 16 : 4;
-    route_sort_small_kernel<<<1, warps * 32, 0, stream>>>(
-        ws, T, E, K, renorm, sb_tile_rows(), T * K / SB_TILE_M + E, out_idx, static_cast<__nv_bfloat16 *>(out_w),
-        expert_offsets, slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale), tile_table);
+    SB_CUDA_CHECK(launch_pdl(route_sort_small_kernel, dim3(1), dim3(warps * 32), 0, stream,
+                             static_cast<const float *>(ws), T, E, K, renorm, sb_tile_rows(),
+                             T * K / SB_TILE_M + E, out_idx, static_cast<__nv_bfloat16 *>(out_w), expert_offsets,
+                             slot_of_item, item_of_slot, static_cast<__nv_bfloat16 *>(slot_scale), tile_table));
     SB_LAUNCH_CHECK();
     return SB_OK;
   }

@@ -25,6 +25,31 @@ void reset_launch_count();
                         cudaGetErrorString(_e), __FILE__, __LINE__);                 \
   } while (0)
 
+// Programmatic dependent launch: a kernel launched with launch_pdl may start
+// (be scheduled, run its index set-up) while the previous kernel of the stream is
+// still draining, once all of that kernel's CTAs have executed
+// pdl_launch_dependents(); pdl_wait() then blocks until the previous kernel has
+// completed and its writes are visible.  Both are no-ops in a plain launch.
+// Rule for kernels using them: no global memory access before pdl_wait().
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define SB_LAUNCH_CHECK()                                                            \
   do {                                                                               \
     cudaError_t _e = cudaGetLastError();                                             \
