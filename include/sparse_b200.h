@@ -236,7 +236,9 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
  * expert-parallel decode step: ep * tokens per rank); with 0 (unknown) only
  * groups of at most SB_DECODE_MAX_TOKENS rows are streamed and the tensor-core
  * kernel of sb_grouped_swiglu is launched for the rest.  Results as
- * sb_grouped_swiglu up to fp32 summation order.  Replaces
+ * sb_grouped_swiglu up to fp32 summation order.  With `row_dst` (see
+ * sb_ep_resolve_return; may be NULL) routed result rows go to those addresses
+ * instead of `out`.  Replaces
  * `_plain_ep_compute_segment` over the received segments and
  * `_shared_expert_forward` (utils/eval_core.py:11700-11765, 13156-13372,
  * 9455-9463) in decode.
@@ -246,7 +248,8 @@ int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, con
                                 int32_t H, int32_t I, int32_t S, void *hbuf, void *out,
                                 int32_t max_group_rows, const void *shared_x, const void *shared_w13,
                                 const void *shared_w2, const void *shared_scale, int32_t I_shared, int32_t T,
-                                void *shared_h, void *shared_out, int32_t *status, void *stream);
+                                void *shared_h, void *shared_out, const uint64_t *row_dst, int32_t *status,
+                                void *stream);
 
 /*
  * Decode-sized routing (T <= SB_DECODE_MAX_TOKENS, bf16): sb_router_topk and the
@@ -352,8 +355,10 @@ int32_t sb_ep_plan(const int32_t *counts_all, const int32_t *owner, int32_t E, i
 /* The whole send side of a decode-sized step as ONE single-CTA launch:
  * sb_ep_publish_counts, barrier, sb_ep_plan, sb_ep_dispatch, barrier ("every
  * rank's rows have landed"); arguments as in those calls, `owner` the full
- * [ep][E] table, two epochs taken from `epoch_counter`.  Meant for at most a
- * few hundred items (one CTA copies the rows). */
+ * [ep][E] table, two epochs taken from `epoch_counter`.  With `peer_meta`
+ * (may be NULL; then `peer_ret`, `row_dst` are unused) the rows carry return
+ * addresses and sb_ep_resolve_return is done at the end of the same launch.
+ * Meant for at most a few hundred items (one CTA copies the rows). */
 int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,
                                 uint32_t *epoch_counter, const int32_t *owner, int32_t E, int32_t rank,
                                 int32_t ep, int32_t recv_cap, int32_t *dst_base, int32_t *recv_offsets,
@@ -361,18 +366,40 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
                                 const void *item_scale, const int32_t *slot_of_item, int32_t n_items,
                                 int32_t items_per_row, int32_t H, void *const *peer_rows,
                                 void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
-                                int32_t *status, void *stream);
+                                void *const *peer_meta, void *const *peer_ret, int32_t ret_rows,
+                                uint64_t *row_dst, int32_t *status, void *stream);
 
 /* Copy every item's activation row and route weight into its row of the
  * owner's receive buffers (`peer_rows[d]` [recv_cap,H] bf16, `peer_scale[d]`
  * [recv_cap] bf16) and remember where it went (`item_rank`, `item_row` [n_items]).
- * `slot_of_item` / `local_offsets` come from sb_permute on the local items. */
+ * `slot_of_item` / `local_offsets` come from sb_permute on the local items.
+ * With `peer_meta` (int32 [recv_cap] per rank, may be NULL) every row also
+ * carries its return address: (rank << 24) | item index, n_items < 2^24. */
 int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *item_scale,
                        const int32_t *slot_of_item, const int32_t *local_offsets,
                        const int32_t *dst_base, const int32_t *owner, int32_t n_items,
                        int32_t items_per_row, int32_t H, int32_t ep, int32_t recv_cap,
                        void *const *peer_rows, void *const *peer_scale, int32_t *item_rank,
-                       int32_t *item_row, void *stream);
+                       int32_t *item_row, int32_t rank, void *const *peer_meta, void *stream);
+
+/* Fused compute + return transfer of the routed experts.  sb_ep_resolve_return
+ * turns the return addresses of the received rows (`recv_meta`, written by the
+ * senders' sb_ep_dispatch) into device addresses of rows in the senders'
+ * return buffers `peer_ret[s]` ([ret_rows,H] bf16, item order) as mapped on
+ * this GPU; sb_grouped_swiglu_scatter is sb_grouped_swiglu whose down pass
+ * stores every result row to that address (a peer store over NVLink when the
+ * sender is another GPU) while the GEMM is still running, instead of to a
+ * local buffer that the senders read afterwards.  After the next barrier each
+ * sender combines its own return buffer with sb_combine (slot_of_item =
+ * identity).  Replaces the output all-to-all of utils/eval_core.py:15048-15054
+ * together with the segment compute of 13156-13372. */
+int32_t sb_ep_resolve_return(const int32_t *recv_meta, const int32_t *recv_offsets, int32_t E,
+                             void *const *peer_ret, int32_t ep, int32_t ret_rows, int32_t H, int32_t recv_cap,
+                             uint64_t *row_dst, void *stream);
+int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
+                                  const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
+                                  int32_t H, int32_t I, int32_t S, void *hbuf, const uint64_t *row_dst,
+                                  int32_t *status, void *stream);
 
 /* sb_combine with the K rows of a token read from the owners' output buffers
  * (`peer_y[d]` [recv_cap,H] bf16). */

@@ -58,7 +58,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_decode_experts": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32,
                                 vp, vp, vp, vp]),
     "sb_grouped_swiglu_mixed": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp,
-                                      i32, i32, vp, vp, vp, vp]),
+                                      i32, i32, vp, vp, vp, vp, vp]),
     "sb_route_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                               vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
@@ -72,10 +72,13 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, vp, vp]),
     "sb_ep_barrier_seq": (i32, [C.POINTER(vp), i32, i32, vp, vp, vp]),
     "sb_ep_exchange_dispatch": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp,
-                                      vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp, vp, vp]),
+                                      vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp,
+                                      C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),
     "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
-                             C.POINTER(vp), C.POINTER(vp), vp, vp, vp]),
+                             C.POINTER(vp), C.POINTER(vp), vp, vp, i32, C.POINTER(vp), vp]),
+    "sb_ep_resolve_return": (i32, [vp, vp, i32, C.POINTER(vp), i32, i32, i32, i32, vp, vp]),
+    "sb_grouped_swiglu_scatter": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_combine": (i32, [C.POINTER(vp), vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sb_moe_layer_struct_bytes": (sz, []),
     "sb_moe_layer_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),

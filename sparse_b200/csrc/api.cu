@@ -105,7 +105,7 @@ int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, i
   const int light = (tile_table != nullptr && H % 32 == 0 && I % 32 == 0) ? hybrid_rows() : 0;
   if (light == 0)
     return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
-                                      R_cap, H, I, S, hbuf, out, status, 0, max_pairs, stream);
+                                      R_cap, H, I, S, hbuf, out, status, 0, max_pairs, nullptr, stream);
   std::lock_guard<std::recursive_mutex> lock(g_side_mu);
   SideLane *lane = side_lane();
   if (lane == nullptr) return fail(SB_E_CUDA, "sb_grouped_swiglu: cannot create the side stream");
@@ -113,14 +113,14 @@ int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, i
   SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
   int32_t rc = launch_decode_experts(rows, nullptr, 1, tile_table, slot_of_expert, w13, w2, row_scale, H, I, S,
                                      hbuf, out, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status, 1, 0,
-                                     nullptr, lane->stream);
+                                     nullptr, nullptr, lane->stream);
   // the join is recorded even after a failed launch, so the side stream never
   // stays forked from a stream that is being captured
   SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
   int32_t rc2 = SB_OK;
   if (rc == SB_OK)
     rc2 = launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
-                                     H, I, S, hbuf, out, status, light, 0, stream);
+                                     H, I, S, hbuf, out, status, light, 0, nullptr, stream);
   SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
   return rc != SB_OK ? rc : rc2;
 }
@@ -241,7 +241,19 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
     return fail(SB_E_UNSUPPORTED, "sb_decode_experts: at most %d rows for the shared expert", SB_DECODE_MAX_TOKENS);
   return launch_decode_experts(x, item_of_slot, items_per_row, tile_table, slot_of_expert, w13, w2, row_scale,
                                H, I, n_slots, hbuf, y, shared_w13, shared_w2, shared_scale, I_shared, T,
-                               shared_h, shared_out, status, 2, 0, nullptr, static_cast<cudaStream_t>(stream));
+                               shared_h, shared_out, status, 2, 0, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
+                                  const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
+                                  int32_t H, int32_t I, int32_t S, void *hbuf, const uint64_t *row_dst,
+                                  int32_t *status, void *stream) {
+  if (!tile_table || !row_dst) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_scatter: null pointer");
+  if (!sb_w13_interleaved())
+    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_scatter: needs the CTA-pair kernel (SPARSE_B200_GEMM=pair)");
+  return launch_grouped_swiglu_pair(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S, hbuf,
+                                    nullptr, status, 0, 0, reinterpret_cast<const unsigned long long *>(row_dst),
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
@@ -249,9 +261,13 @@ int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, con
                                 int32_t H, int32_t I, int32_t S, void *hbuf, void *out,
                                 int32_t max_group_rows, const void *shared_x, const void *shared_w13,
                                 const void *shared_w2, const void *shared_scale, int32_t I_shared, int32_t T,
-                                void *shared_h, void *shared_out, int32_t *status, void *stream) {
+                                void *shared_h, void *shared_out, const uint64_t *row_dst, int32_t *status,
+                                void *stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!tile_table) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: needs a tile table");
+  const unsigned long long *dst = reinterpret_cast<const unsigned long long *>(row_dst);
+  if (dst != nullptr && !sb_w13_interleaved())
+    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_mixed: row_dst needs the CTA-pair kernel build");
   const bool with_shared = shared_w13 != nullptr && T > 0;
   if (with_shared && (!shared_x || !shared_w2 || !shared_h || !shared_out || I_shared <= 0))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: shared expert arguments go together");
@@ -267,10 +283,10 @@ int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, con
                                      hbuf, out, with_shared ? shared_w13 : nullptr,
                                      with_shared ? shared_w2 : nullptr, with_shared ? shared_scale : nullptr,
                                      with_shared ? I_shared : 0, with_shared ? T : 1, shared_h, shared_out,
-                                     status, 2, limit, shared_x, st);
+                                     status, 2, limit, shared_x, dst, st);
   if (rc != SB_OK || max_group_rows > 0) return rc;     // the caller's bound says no group is left over
   return launch_grouped_swiglu_pair(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S,
-                                    hbuf, out, status, limit, 0, st);
+                                    hbuf, out, status, limit, 0, dst, st);
 }
 
 int32_t sb_route_decode(const void *x, const void *w_router, const float *router_bias, const void *w_shared_gate,
@@ -355,7 +371,7 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     rc = launch_decode_experts(L->x, s.item_of_slot, K, s.tile_table, L->slot_of_expert, L->w13, L->w2,
                                s.slot_scale, H, I, L->n_slots, s.hbuf, s.y, Is > 0 ? L->shared_w13 : nullptr,
                                Is > 0 ? L->shared_w2 : nullptr, L->shared_gate_w ? s.shared_scale : nullptr,
-                               Is, T, s.shared_h, s.shared_out, status, 2, 0, nullptr, stream);
+                               Is, T, s.shared_h, s.shared_out, status, 2, 0, nullptr, nullptr, stream);
     if (rc != SB_OK) return rc;
     return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                           L->out, stream);

@@ -209,7 +209,7 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
                    __nv_bfloat16 *__restrict__ y, const __nv_bfloat16 *__restrict__ shared_h,
                    const __nv_bfloat16 *__restrict__ shared_w2, const __nv_bfloat16 *__restrict__ shared_scale,
                    int I_sh, int T, __nv_bfloat16 *__restrict__ shared_out, int ks_routed, int ks_shared,
-                   int max_rows) {
+                   int max_rows, const unsigned long long *__restrict__ row_dst) {
   __shared__ float red[kWarps][8][32];
   pdl_launch_dependents();
   pdl_wait();
@@ -272,13 +272,16 @@ decode_down_kernel(const __nv_bfloat16 *__restrict__ hbuf, const int32_t *__rest
           const int t = nt * 8 + 2 * c + i;
           if (t < n_tok) {
             const float sc = scale != nullptr ? __bfloat162float(scale[begin + t]) : 1.0f;
+            // routed rows may have a destination of their own (the sender's return buffer)
+            __nv_bfloat16 *orow = out + (size_t)(begin + t) * H;
+            if (!is_shared && row_dst != nullptr) orow = reinterpret_cast<__nv_bfloat16 *>(row_dst[begin + t]);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               const int n = n0 + half * 8 + g;
-              if (n < H) {
+              if (n < H && orow != nullptr) {
                 float v = round_bf16(acc[nt][half * 2 + i]);
                 if (scale != nullptr) v *= sc;
-                out[(size_t)(begin + t) * H + n] = __float2bfloat16_rn(v);
+                orow[n] = __float2bfloat16_rn(v);
               }
             }
           }
@@ -295,13 +298,14 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
                               void *y, const void *shared_w13, const void *shared_w2, const void *shared_scale,
                               int I_sh, int T, void *shared_h, void *shared_out, int32_t *status,
-                              int ctas_per_sm, int max_rows, const void *shared_x, cudaStream_t stream) {
+                              int ctas_per_sm, int max_rows, const void *shared_x,
+                              const unsigned long long *row_dst, cudaStream_t stream) {
   if (H % 32 != 0 || I % 32 != 0 || I_sh % 32 != 0)
     return fail(SB_E_UNSUPPORTED, "sb_decode_experts: H, I, I_shared must be multiples of 32");
   if (max_rows <= 0) max_rows = kMaxTok;
   if (shared_x == nullptr) shared_x = x;
   if (T <= 0) return SB_OK;
-  if (!x || (tile_table && (!w13 || !w2 || !hbuf || !y)))
+  if (!x || (tile_table && (!w13 || !w2 || !hbuf || (!y && !row_dst))))
     return fail(SB_E_INVALID_ARG, "sb_decode_experts: null pointer");
   if ((shared_w13 != nullptr) != (shared_w2 != nullptr) || (shared_w13 && (!shared_h || !shared_out)))
     return fail(SB_E_INVALID_ARG, "sb_decode_experts: shared expert arguments go together");
@@ -332,7 +336,7 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
       static_cast<const __nv_bfloat16 *>(w2), static_cast<const __nv_bfloat16 *>(row_scale), H, I, n_slots,
       static_cast<__nv_bfloat16 *>(y), static_cast<const __nv_bfloat16 *>(shared_h),
       static_cast<const __nv_bfloat16 *>(shared_w2), static_cast<const __nv_bfloat16 *>(shared_scale), I_sh, T,
-      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, max_rows));
+      static_cast<__nv_bfloat16 *>(shared_out), ks2_routed, ks2_shared, max_rows, row_dst));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

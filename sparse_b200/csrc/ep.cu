@@ -189,7 +189,8 @@ __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const
                                               int n_items, int items_per_row, int vec_per_row, int recv_cap,
                                               const PeerPtrs &recv_rows, const PeerPtrs &recv_scale,
                                               int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
-                                              int first_warp, int warps_total) {
+                                              int first_warp, int warps_total, int rank = 0,
+                                              const PeerPtrs *recv_meta = nullptr) {
   const int lane = threadIdx.x & 31;
   for (int i = first_warp; i < n_items; i += warps_total) {
     const int e = item_expert[i];
@@ -209,6 +210,8 @@ __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const
     for (int v = lane; v < vec_per_row; v += 32) dp[v] = __ldg(s + v);
     if (lane == 0) {
       static_cast<__nv_bfloat16 *>(recv_scale.p[d])[row] = item_scale[i];
+      // return address of the row: sender rank and the sender's item index
+      if (recv_meta != nullptr) static_cast<int32_t *>(recv_meta->p[d])[row] = (rank << 24) | i;
       item_rank[i] = d; item_row[i] = row;
     }
   }
@@ -220,10 +223,35 @@ ep_dispatch_kernel(const uint4 *__restrict__ x, const int32_t *__restrict__ item
                    const int32_t *__restrict__ slot_of_item, const int32_t *__restrict__ local_offsets,
                    const int32_t *__restrict__ dst_base, const int32_t *__restrict__ owner,
                    int n_items, int items_per_row, int vec_per_row, int recv_cap, PeerPtrs recv_rows,
-                   PeerPtrs recv_scale, int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row) {
+                   PeerPtrs recv_scale, int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
+                   int rank, int with_meta, PeerPtrs recv_meta) {
   dispatch_body(x, item_expert, item_scale, slot_of_item, local_offsets, dst_base, owner, n_items, items_per_row,
                 vec_per_row, recv_cap, recv_rows, recv_scale, item_rank, item_row,
-                blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), gridDim.x * (blockDim.x >> 5));
+                blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), gridDim.x * (blockDim.x >> 5), rank,
+                with_meta ? &recv_meta : nullptr);
+}
+
+// For every received row: the address of its row in the sender's return buffer,
+// as seen from this GPU (what the scatter epilogue of the down GEMM stores to).
+__device__ __forceinline__ void resolve_body(const volatile int32_t *recv_meta, int total, const PeerPtrs &ret,
+                                             int ep, int ret_rows, size_t row_bytes,
+                                             unsigned long long *__restrict__ row_dst, int first, int stride) {
+  for (int r = first; r < total; r += stride) {
+    const int m = recv_meta[r];
+    const int s = (m >> 24) & 0xff, i = m & 0xffffff;
+    unsigned long long d = 0ull;
+    if (s < ep && i < ret_rows)
+      d = reinterpret_cast<unsigned long long>(static_cast<char *>(ret.p[s]) + (size_t)i * row_bytes);
+    row_dst[r] = d;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ep_resolve_return_kernel(const int32_t *__restrict__ recv_meta, const int32_t *__restrict__ recv_offsets, int E,
+                         PeerPtrs ret, int ep, int ret_rows, size_t row_bytes,
+                         unsigned long long *__restrict__ row_dst) {
+  resolve_body(recv_meta, recv_offsets[E], ret, ep, ret_rows, row_bytes, row_dst,
+               blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
 }
 
 // The whole send side of a decode-sized step in ONE single-CTA launch: counts
@@ -238,7 +266,8 @@ ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs 
                             const int32_t *__restrict__ slot_of_item, int n_items, int items_per_row,
                             int vec_per_row, int recv_cap, PeerPtrs recv_rows, PeerPtrs recv_scale,
                             int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
-                            int32_t *__restrict__ status) {
+                            int32_t *__restrict__ status, int with_meta, PeerPtrs recv_meta, PeerPtrs ret,
+                            int ret_rows, unsigned long long *__restrict__ row_dst) {
   extern __shared__ int plan_smem[];
   publish_body(local_offsets, E, rank, ep, counts_all);
   __threadfence_system();
@@ -250,10 +279,17 @@ ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs 
   __syncthreads();                      // dst_base (global, written by this CTA) is visible to all its threads
   dispatch_body(x, item_expert, item_scale, slot_of_item, local_offsets, dst_base, owner + (size_t)rank * E,
                 n_items, items_per_row, vec_per_row, recv_cap, recv_rows, recv_scale, item_rank, item_row,
-                threadIdx.x >> 5, blockDim.x >> 5);
+                threadIdx.x >> 5, blockDim.x >> 5, rank, with_meta ? &recv_meta : nullptr);
   __threadfence_system();
   epoch = next_epoch(epoch_counter);
   barrier_body(flags, rank, ep, epoch, status);
+  if (with_meta) {
+    // every rank's rows and return addresses have landed: resolve them
+    __syncthreads();
+    resolve_body(static_cast<const int32_t *>(recv_meta.p[rank]),
+                 *reinterpret_cast<const volatile int32_t *>(recv_offsets + E), ret, ep, ret_rows,
+                 (size_t)vec_per_row * 16, row_dst, threadIdx.x, blockDim.x);
+  }
 }
 
 __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
@@ -414,7 +450,8 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
                                 const void *item_scale, const int32_t *slot_of_item, int32_t n_items,
                                 int32_t items_per_row, int32_t H, void *const *peer_rows,
                                 void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
-                                int32_t *status, void *stream) {
+                                void *const *peer_meta, void *const *peer_ret, int32_t ret_rows,
+                                uint64_t *row_dst, int32_t *status, void *stream) {
   if (!local_offsets || !epoch_counter || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 ||
       E > kMaxExperts || rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
     return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
@@ -428,6 +465,15 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
   if ((rc = fill_peers(&pf, peer_flags, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
   if ((rc = fill_peers(&pr, peer_rows, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
   if ((rc = fill_peers(&ps, peer_scale, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  PeerPtrs pm, pt;
+  for (int i = 0; i < kMaxRanks; ++i) { pm.p[i] = nullptr; pt.p[i] = nullptr; }
+  const int with_meta = peer_meta != nullptr ? 1 : 0;
+  if (with_meta) {
+    if (!peer_ret || !row_dst || ret_rows < 0 || n_items >= (1 << 24))
+      return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: return-address arguments go together");
+    if ((rc = fill_peers(&pm, peer_meta, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+    if ((rc = fill_peers(&pt, peer_ret, ep, "sb_ep_exchange_dispatch")) != SB_OK) return rc;
+  }
   const int tile_cap = recv_cap / SB_TILE_M + E;
   const size_t smem = ((size_t)2 * ep * E + 2 * (size_t)(E + 1)) * sizeof(int);
   if (smem > 48 * 1024)
@@ -436,7 +482,8 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
   ep_exchange_dispatch_kernel<<<1, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       local_offsets, pc, pf, epoch_counter, owner, E, rank, ep, tile_cap, sb_tile_rows(), dst_base, recv_offsets,
       tile_table, static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),
-      slot_of_item, n_items, items_per_row, H / 8, recv_cap, pr, ps, item_rank, item_row, status);
+      slot_of_item, n_items, items_per_row, H / 8, recv_cap, pr, ps, item_rank, item_row, status, with_meta, pm,
+      pt, ret_rows, reinterpret_cast<unsigned long long *>(row_dst));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -463,24 +510,46 @@ int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *it
                        const int32_t *dst_base, const int32_t *owner, int32_t n_items,
                        int32_t items_per_row, int32_t H, int32_t ep, int32_t recv_cap,
                        void *const *peer_rows, void *const *peer_scale, int32_t *item_rank,
-                       int32_t *item_row, void *stream) {
-  if (n_items < 0 || H <= 0 || H % 8 != 0 || items_per_row < 1)
-    return fail(SB_E_INVALID_ARG, "sb_ep_dispatch: bad shape (n=%d H=%d)", n_items, H);
+                       int32_t *item_row, int32_t rank, void *const *peer_meta, void *stream) {
+  if (n_items < 0 || H <= 0 || H % 8 != 0 || items_per_row < 1 || n_items >= (1 << 24) || rank < 0 || rank >= ep)
+    return fail(SB_E_INVALID_ARG, "sb_ep_dispatch: bad shape (n=%d H=%d rank=%d)", n_items, H, rank);
   if (n_items == 0) return SB_OK;
   if (!x || !item_expert || !item_scale || !slot_of_item || !local_offsets || !dst_base || !owner ||
       !item_rank || !item_row)
     return fail(SB_E_INVALID_ARG, "sb_ep_dispatch: null pointer");
-  PeerPtrs pr, ps;
+  PeerPtrs pr, ps, pm;
   int32_t rc;
   if ((rc = fill_peers(&pr, peer_rows, ep, "sb_ep_dispatch")) != SB_OK) return rc;
   if ((rc = fill_peers(&ps, peer_scale, ep, "sb_ep_dispatch")) != SB_OK) return rc;
+  for (int i = 0; i < kMaxRanks; ++i) pm.p[i] = nullptr;
+  if (peer_meta != nullptr && (rc = fill_peers(&pm, peer_meta, ep, "sb_ep_dispatch")) != SB_OK) return rc;
   int blocks = (n_items + 7) / 8;
   const int max_blocks = sb_device_sm_count() * 8;
   if (blocks > max_blocks) blocks = max_blocks;
   ep_dispatch_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),
       slot_of_item, local_offsets, dst_base, owner, n_items, items_per_row, H / 8, recv_cap, pr, ps,
-      item_rank, item_row);
+      item_rank, item_row, rank, peer_meta != nullptr ? 1 : 0, pm);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_resolve_return(const int32_t *recv_meta, const int32_t *recv_offsets, int32_t E,
+                             void *const *peer_ret, int32_t ep, int32_t ret_rows, int32_t H, int32_t recv_cap,
+                             uint64_t *row_dst, void *stream) {
+  if (!recv_meta || !recv_offsets || !row_dst || E < 1 || E > kMaxExperts || ret_rows < 0 || H <= 0 ||
+      recv_cap < 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_resolve_return: bad arguments");
+  PeerPtrs pr;
+  int32_t rc = fill_peers(&pr, peer_ret, ep, "sb_ep_resolve_return");
+  if (rc != SB_OK) return rc;
+  int blocks = (recv_cap + 255) / 256;
+  const int max_blocks = sb_device_sm_count() * 4;
+  if (blocks > max_blocks) blocks = max_blocks;
+  if (blocks < 1) blocks = 1;
+  ep_resolve_return_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      recv_meta, recv_offsets, E, pr, ep, ret_rows, (size_t)H * 2,
+      reinterpret_cast<unsigned long long *>(row_dst));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

@@ -200,7 +200,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                  const int32_t *__restrict__ tile_table, int dense_rows,
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
-                 int32_t *__restrict__ status, int skip_rows_upto, int dense_chunk, int light_max) {
+                 int32_t *__restrict__ status, int skip_rows_upto, int dense_chunk, int light_max,
+                 const unsigned long long *__restrict__ row_dst) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -364,12 +365,27 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           float my_scale = 1.0f;
           if (row_scale != nullptr && c0 + lane < n_tok)
             my_scale = __bfloat162float(row_scale[ch.tok_begin + c0 + lane]);
-          __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
+          if (row_dst == nullptr) {
+            __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float sc = __shfl_sync(0xffffffffu, my_scale, j);
-            const float y = round_bf16(__uint_as_float(v[j])) * sc;
-            if (col_ok && c0 + j < n_tok) obase[(size_t)j * ld_out] = __float2bfloat16_rn(y);
+            for (int j = 0; j < 32; ++j) {
+              const float sc = __shfl_sync(0xffffffffu, my_scale, j);
+              const float y = round_bf16(__uint_as_float(v[j])) * sc;
+              if (col_ok && c0 + j < n_tok) obase[(size_t)j * ld_out] = __float2bfloat16_rn(y);
+            }
+          } else {
+            // Scatter: every row goes straight to the address its sender asked for
+            // (a row of the sender's return buffer, possibly on another GPU), so
+            // the transfer back overlaps the GEMM instead of following it.
+            unsigned long long my_dst = 0ull;
+            if (c0 + lane < n_tok) my_dst = row_dst[ch.tok_begin + c0 + lane];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float sc = __shfl_sync(0xffffffffu, my_scale, j);
+              const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, j);
+              const float y = round_bf16(__uint_as_float(v[j])) * sc;
+              if (col_ok && d != 0ull) reinterpret_cast<__nv_bfloat16 *>(d)[wrow] = __float2bfloat16_rn(y);
+            }
           }
         }
       }
@@ -436,7 +452,8 @@ int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, ui
 template <int MODE>
 int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
-                    int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto, cudaStream_t stream) {
+                    int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto,
+                    const unsigned long long *row_dst, cudaStream_t stream) {
   // Dense rows are cut into chunks of kMaxN tokens.  (Smaller chunks give more
   // tiles for a small batch but were slower on B200: every chunk re-streams the
   // whole weight tile from L2.)
@@ -452,7 +469,7 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
                                               slot_of_expert,
                                               static_cast<const __nv_bfloat16 *>(row_scale),
                                               static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
-                                              status, skip_rows_upto, dense_chunk, probe_light);
+                                              status, skip_rows_upto, dense_chunk, probe_light, row_dst);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -462,19 +479,22 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
 // w13 must be in the INTERLEAVED row order (row 2j = gate_j, row 2j+1 = up_j);
 // tile_table must have been built with 256-row tiles.  Tile entries of at most
 // `skip_rows_upto` rows are left to the caller (0 = none); `max_pairs` > 0
-// limits the grid to that many CTA pairs.
+// limits the grid to that many CTA pairs.  With `row_dst` (one device address per
+// row, 0 = drop) the down pass writes each result row to that address instead
+// of `out`.
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
-                                   int skip_rows_upto, int max_pairs, cudaStream_t stream) {
+                                   int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
+                                   cudaStream_t stream) {
   if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
     return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
   if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
   if (tile_table == nullptr && (dense_rows < 0 || dense_rows > R_cap))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: dense_rows=%d outside [0,%d]", dense_rows, R_cap);
   if (tile_table == nullptr && dense_rows == 0) return SB_OK;
-  if (!rows || !w13 || !w2 || !hbuf || !out) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
-  if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || !aligned(out, 16))
+  if (!rows || !w13 || !w2 || !hbuf || (!out && !row_dst)) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
+  if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || (out && !aligned(out, 16)))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
   CUtensorMap tm_x[3], tm_w13, tm_h[3], tm_w2;
   const uint32_t boxes[3] = {128, 64, 16};
@@ -489,10 +509,10 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
   if (max_pairs > 0 && 2 * max_pairs < grid) grid = 2 * max_pairs;     // leave the other SMs to a concurrent launch
   rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
-                                H / kBlockK, S, status, grid, skip_rows_upto, stream);
+                                H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stream);
   if (rc != SB_OK) return rc;
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
-                                 I / kBlockK, S, status, grid, skip_rows_upto, stream);
+                                 I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stream);
 }
 
 }  // namespace sb

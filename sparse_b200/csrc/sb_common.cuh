@@ -108,14 +108,15 @@ int32_t launch_grouped_swiglu(const void *rows, const int32_t *tile_table, int d
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows,
                                    const void *w13, const void *w2, const int32_t *slot_of_expert,
                                    const void *row_scale, int R_cap, int H, int I, int S,
-                                   void *hbuf, void *out, int32_t *status, int skip_rows_upto, int max_pairs, cudaStream_t stream);
+                                   void *hbuf, void *out, int32_t *status, int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
+                                   cudaStream_t stream);
 int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int items_per_row,
                               const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,
                               void *y, const void *shared_w13, const void *shared_w2,
                               const void *shared_scale, int I_sh, int T, void *shared_h, void *shared_out,
                               int32_t *status, int ctas_per_sm, int max_rows, const void *shared_x,
-                              cudaStream_t stream);
+                              const unsigned long long *row_dst, cudaStream_t stream);
 int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
                        const void *shared_out, int T, int H, int K, void *out,
                        cudaStream_t stream);

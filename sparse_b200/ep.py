@@ -86,14 +86,19 @@ def plan_layout_reference(counts_all: torch.Tensor, owner: torch.Tensor, rank: i
 class PeerBuffers:
     """This rank's exportable buffers and the pointers of every rank's copies."""
 
-    NAMES = ("rows", "scale", "y", "ctl")
+    NAMES = ("rows", "scale", "y", "ctl", "meta", "ret")
 
-    def __init__(self, hidden: int, num_experts: int, recv_cap: int, ep: int, rank: int):
+    def __init__(self, hidden: int, num_experts: int, recv_cap: int, ep: int, rank: int, ret_rows: int = 0):
         self.hidden, self.num_experts, self.recv_cap, self.ep, self.rank = hidden, num_experts, recv_cap, ep, rank
+        # rows of the return buffer: this rank's own items (tokens * top_k)
+        self.ret_rows = ret_rows if ret_rows > 0 else max(1, recv_cap // ep)
         self.sizes = {
             "rows": recv_cap * hidden * 2,
             "scale": _round_up(recv_cap * 2, 256),
             "y": recv_cap * hidden * 2,
+            # return address of every received row, and the buffer the owners write results back into
+            "meta": _round_up(recv_cap * 4, 256),
+            "ret": self.ret_rows * hidden * 2,
             # counts matrix int32 [ep][E] followed (at a 256-byte boundary) by the barrier flags uint32 [ep]
             "ctl": _round_up(ep * num_experts * 4, 256) + 256,
         }
@@ -200,9 +205,16 @@ class EpRank:
         self.launches = 0
         self._x = None
         self._t = 0
+        self._scattered = False
         # Batches of at most DECODE_MAX_TOKENS rows take the decode-sized kernels
         # (per-row router, single-CTA sort, weight-streaming expert kernels).
         self.small_batch_kernels = True
+        # Owners write result rows straight into the senders' return buffers from
+        # the down GEMM's epilogue (needs the CTA-pair kernel); otherwise senders
+        # read the owners' output buffers after the GEMM.
+        self.scatter_return = bool(lib.sb_w13_interleaved())
+        self.row_dst = torch.zeros((bufs.recv_cap,), dtype=torch.int64, device=dev)
+        self.identity = torch.arange(max(n, 1), dtype=i32, device=dev)
         self.route_ws = torch.empty((_lib.DECODE_MAX_TOKENS * e,), dtype=torch.float32, device=dev)
         self.local_scale = torch.empty((max(_lib.DECODE_MAX_TOKENS * top_k, 1),), dtype=bf, device=dev)
 
@@ -268,8 +280,12 @@ class EpRank:
             b.recv_cap, self.dst_base.data_ptr(), self.recv_offsets.data_ptr(), self.recv_tiles.data_ptr(),
             self._x.data_ptr(), self.topk_idx.data_ptr(), self.topk_w.data_ptr(), self.slot_of_item.data_ptr(),
             t * k, k, w.hidden, b.ptr_array("rows"), b.ptr_array("scale"), self.item_rank.data_ptr(),
-            self.item_row.data_ptr(), self.status.data_ptr(), self._s()), "sb_ep_exchange_dispatch")
+            self.item_row.data_ptr(), b.ptr_array("meta") if self.scatter_return else None,
+            b.ptr_array("ret") if self.scatter_return else None, b.ret_rows,
+            self.row_dst.data_ptr() if self.scatter_return else None, self.status.data_ptr(), self._s()),
+            "sb_ep_exchange_dispatch")
         self.launches += 1
+        self._scattered = self.scatter_return
 
     def stage_experts_and_shared(self) -> None:
         """Routed groups and the shared expert in one pair of weight-streaming launches."""
@@ -284,7 +300,8 @@ class EpRank:
             self.shared_scale.data_ptr() if has_shared and w.shared_gate_w is not None else None,
             w.shared_inter if has_shared else 0, t if has_shared else 0,
             self.shared_h.data_ptr() if has_shared else None, self.shared_out.data_ptr() if has_shared else None,
-            self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed")
+            self.row_dst.data_ptr() if self._scattered else None, self.status.data_ptr(), self._s()),
+            "sb_grouped_swiglu_mixed")
         self.launches += 2
 
     def stage_plan(self) -> None:
@@ -301,8 +318,10 @@ class EpRank:
             self.slot_of_item.data_ptr(), self.local_offsets.data_ptr(), self.dst_base.data_ptr(),
             self.owner_row.data_ptr(), t * k, k, w.hidden, self.ep, self.bufs.recv_cap,
             self.bufs.ptr_array("rows"), self.bufs.ptr_array("scale"), self.item_rank.data_ptr(),
-            self.item_row.data_ptr(), self._s()), "sb_ep_dispatch")
+            self.item_row.data_ptr(), self.rank, self.bufs.ptr_array("meta") if self.scatter_return else None,
+            self._s()), "sb_ep_dispatch")
         self.launches += 1
+        self._scattered = self.scatter_return
 
     def stage_shared(self) -> None:
         w, t = self.w, self._t
@@ -324,16 +343,34 @@ class EpRank:
             self.status.data_ptr(), self._s()), "sb_grouped_swiglu(shared)")
         self.launches += 2
 
+    def stage_resolve(self) -> None:
+        """After every rank's rows (and return addresses) have landed."""
+        if not self._scattered:
+            return
+        b = self.bufs
+        check(lib.sb_ep_resolve_return(b.local["meta"], self.recv_offsets.data_ptr(), self.w.num_experts,
+                                       b.ptr_array("ret"), self.ep, b.ret_rows, self.w.hidden, b.recv_cap,
+                                       self.row_dst.data_ptr(), self._s()), "sb_ep_resolve_return")
+        self.launches += 1
+
     def stage_experts(self) -> None:
         w, b = self.w, self.bufs
+        dst = self.row_dst.data_ptr() if self._scattered else None
         if self._small():
             # few rows per expert arrive in a decode step, whatever the peers sent
             check(lib.sb_grouped_swiglu_mixed(
                 b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
                 w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
                 self.hbuf.data_ptr(), b.local["y"], 0, None, None, None, None, 0, 0, None, None,
-                self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed(routed)")
+                dst, self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed(routed)")
             self.launches += 4
+            return
+        if self._scattered:
+            check(lib.sb_grouped_swiglu_scatter(
+                b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
+                w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
+                self.hbuf.data_ptr(), dst, self.status.data_ptr(), self._s()), "sb_grouped_swiglu_scatter")
+            self.launches += 2
             return
         check(lib.sb_grouped_swiglu(
             b.local["rows"], self.recv_tiles.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
@@ -345,6 +382,13 @@ class EpRank:
     def stage_combine(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         w, t, k = self.w, self._t, self.top_k
         dst = self.out[:t] if out is None else out
+        if self._scattered:
+            # every row of this rank's items is already here, in item order
+            check(lib.sb_combine(self.bufs.local["ret"], self.identity.data_ptr(), self.topk_idx.data_ptr(),
+                                 self.shared_out.data_ptr() if w.shared_inter else None, t, w.hidden, k,
+                                 dst.data_ptr(), self._s()), "sb_combine")
+            self.launches += 1
+            return dst
         check(lib.sb_ep_combine(
             self.bufs.ptr_array("y"), self.item_rank.data_ptr(), self.item_row.data_ptr(),
             self.topk_idx.data_ptr(), self.shared_out.data_ptr() if w.shared_inter else None, t,
@@ -423,14 +467,13 @@ class ExpertParallelLayer:
                 r.stage_shared()
                 mark("shared_swiglu")
                 self._barrier()
+                r.stage_resolve()
                 mark("barrier(rows landed)")
             elif x.shape[0] <= _lib.DECODE_MAX_TOKENS and r.small_batch_kernels:
                 # Decode-sized step: launch-bound, so one stream, the fewest
                 # launches, nothing that a CUDA graph capture could not record.
-                # Every rank of the group must take this branch in the same step
-                # (the fused kernel runs two barriers): callers keep decode
-                # batches within DECODE_MAX_TOKENS rows on all ranks, or set
-                # small_batch_kernels = False everywhere.
+                # Ranks may take different branches in the same step: every branch
+                # runs three barriers and uses the same return protocol.
                 r.stage_route(x)
                 r.stage_exchange_dispatch()
                 r.stage_experts_and_shared()
@@ -451,6 +494,7 @@ class ExpertParallelLayer:
                     r.stage_plan()
                     r.stage_dispatch()
                     self._barrier()
+                    r.stage_resolve()
                     self._join.record(self._side)
                 r.stage_shared()
                 stream.wait_event(self._join)

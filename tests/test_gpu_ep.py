@@ -74,6 +74,7 @@ def test_simulated_ranks_match_single_gpu(shape_name, ep, tokens, small):
             ranks[r].stage_shared()
         torch.cuda.synchronize()
         for r in range(ep):
+            ranks[r].stage_resolve()
             ranks[r].stage_experts()
         torch.cuda.synchronize()
         outs = [ranks[r].stage_combine().clone() for r in range(ep)]
@@ -171,6 +172,7 @@ def test_simulated_ranks_with_replicated_placement():
             ranks[r].stage_plan(); ranks[r].stage_dispatch(); ranks[r].stage_shared()
         torch.cuda.synchronize()
         for r in range(ep):
+            ranks[r].stage_resolve()
             ranks[r].stage_experts()
         torch.cuda.synchronize()
         got = torch.cat([ranks[r].stage_combine().clone() for r in range(ep)])
