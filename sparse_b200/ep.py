@@ -516,3 +516,47 @@ class ExpertParallelLayer:
             self.r.status.zero_()
             raise RuntimeError("sparse_b200 EP device status %d (1: GEMM wait expired, 2: expert "
                                "without a weight slot, 3: peer barrier wait expired)" % s)
+
+
+class CachedExpertParallelLayer(ExpertParallelLayer):
+    """Expert-parallel layer whose owned experts live in pinned host memory with
+    an LRU of device slots (`store.ExpertStore`), as the reference runs with
+    `expert_offload="cpu"` under EP (utils/eval_core.py:13156-13372 over
+    11338-11435).  The received rows are known on the device only, so after the
+    "rows landed" barrier the E+1 receive offsets are read back once (the
+    reference synchronises per segment) and the experts with rows are made
+    resident and run in as few grouped launches as the cache allows, in EPIPE's
+    readiness order when that is enabled.  One stream, stage after stage."""
+
+    def __init__(self, cached_runner, top_k: int, max_tokens: int, rank: int, ep: int, process_group,
+                 owner=None, renorm: bool = False, fp32_logits: bool = False):
+        super().__init__(cached_runner.store.w, top_k, max_tokens, rank, ep, process_group, owner=owner,
+                         renorm=renorm, fp32_logits=fp32_logits)
+        self.cached = cached_runner
+        self.r.status = cached_runner.status          # one status word for both
+        self.overlap = False
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, stage: str = "") -> torch.Tensor:
+        from .context import SparseContext
+        r, c = self.r, self.cached
+        r.launches = 0
+        t = x.shape[0]
+        stage = stage or SparseContext.stage(1 if t == 1 else t)
+        with torch.cuda.device(r.device):
+            r.stage_route(x)
+            r.stage_publish()
+            self._barrier()
+            r.stage_plan()
+            r.stage_dispatch()
+            r.stage_shared()
+            self._barrier()
+            r.stage_resolve()
+            needed = c._needed_experts(r.recv_offsets)      # the one host synchronisation
+            c.last_needed = needed
+            plan = c._epipe_plan(needed, stage)
+            c.last_plan = plan
+            c.run_routed(needed, r.stage_experts, plan)
+            self._barrier()
+            res = r.stage_combine(out)
+        self.last_launches = r.launches
+        return res

@@ -125,8 +125,6 @@ class DistributedSparseMoeBlock(nn.Module):
         self._ep = None
         fp32_logits = self.moe_family == "deepseek_shared"
         if offloaded:
-            if self.comm_world > 1:
-                raise NotImplementedError("expert_offload=cpu with ep_size>1 is not built yet; use expert_offload=gpu")
             host = HostExperts(self.hidden_size, inter)
             for e in local:
                 g, u, d = _expert_matrices(mlp_block.experts, e)
@@ -136,6 +134,12 @@ class DistributedSparseMoeBlock(nn.Module):
             self.store.push_slot_map()
             self._cached = CachedLayerRunner(self.store, top_k, renorm=self.norm_topk_prob, fp32_logits=fp32_logits)
             self._cache = self.store.cache
+            if self.comm_world > 1:
+                from .ep import CachedExpertParallelLayer
+                table = self.placement.dest_table(self.layer_idx, "prefill")
+                self._ep = CachedExpertParallelLayer(self._cached, top_k, max_tokens, self.comm_rank,
+                                                     self.comm_world, process_group, owner=table,
+                                                     renorm=self.norm_topk_prob, fp32_logits=fp32_logits)
         else:
             slot_of = [-1] * num_experts
             for slot, e in enumerate(local):
@@ -207,11 +211,11 @@ class DistributedSparseMoeBlock(nn.Module):
         SparseContext.current_moe_layer_idx = self.layer_idx
         stage = SparseContext.stage(s)
         self._compute_and_schedule_next_layer_rs(x, s)
-        if self._cached is not None:
-            out, idx, wts, logits = self._cached.forward(x, stage)
-        elif self._ep is not None:
-            out = self._ep.forward(x).clone()
+        if self._ep is not None:
+            out = (self._ep.forward(x, stage=stage) if self._cached is not None else self._ep.forward(x)).clone()
             logits = self._ep.logits[:x.shape[0]]
+        elif self._cached is not None:
+            out, idx, wts, logits = self._cached.forward(x, stage)
         else:
             out, idx, wts, logits = self._runner.forward(x)
             out = out.clone()

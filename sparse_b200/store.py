@@ -394,51 +394,11 @@ class CachedLayerRunner:
                 metrics.epipe_ready_group_count += len(plan.first)
         return plan
 
-    def forward(self, x: torch.Tensor, stage: str = "") -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-        st, w, k = self.store, self.store.w, self.top_k
-        t = x.shape[0]
-        stage = stage or SparseContext.stage(1 if t == 1 else t)
-        idx, wts, logits, shared_scale = ops.router_topk(
-            x, w.router_w, k, bias=w.router_bias, w_shared_gate=w.shared_gate_w, renorm=self.renorm,
-            fp32_logits=self.fp32_logits)
-        p = ops.permute(x, idx.reshape(-1), w.num_experts, k, item_scale=wts.reshape(-1))
-        needed = self._needed_experts(p.expert_offsets)
-        self.last_needed = needed
-        plan = self._epipe_plan(needed, stage)
-        self.last_plan = plan
-        hbuf = torch.empty((p.r_cap, w.inter), dtype=torch.bfloat16, device=w.device)
-        y = torch.empty((p.r_cap, w.hidden), dtype=torch.bfloat16, device=w.device)
-
-        # Up to DECODE_MAX_TOKENS rows take the same weight-streaming kernels the
-        # resident layer uses at that size, so both stay bit-identical; the
-        # shared expert rides in the first of those launches.
-        decode = t <= DECODE_MAX_TOKENS
-        shared_h = shared_dec = None
-        if decode and w.shared_inter:
-            shared_h = torch.empty((t, w.shared_inter), dtype=torch.bfloat16, device=w.device)
-            shared_dec = torch.empty((t, w.hidden), dtype=torch.bfloat16, device=w.device)
-        shared_pending = [decode and bool(w.shared_inter)]
-
-        def gemm():
-            stream = torch.cuda.current_stream(w.device).cuda_stream
-            if decode:
-                with_shared = shared_pending[0]
-                shared_pending[0] = False
-                _lib.check(_lib.lib.sb_decode_experts(
-                    x.data_ptr(), p.item_of_slot.data_ptr(), k, p.tile_table.data_ptr(),
-                    w.slot_of_expert.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(), p.slot_scale.data_ptr(),
-                    w.hidden, w.inter, w.n_slots, hbuf.data_ptr(), y.data_ptr(),
-                    w.shared_w13.data_ptr() if with_shared else 0, w.shared_w2.data_ptr() if with_shared else 0,
-                    shared_scale.data_ptr() if with_shared and shared_scale is not None else 0,
-                    w.shared_inter if with_shared else 0, t,
-                    shared_h.data_ptr() if with_shared else 0, shared_dec.data_ptr() if with_shared else 0,
-                    self.status.data_ptr(), stream), "sb_decode_experts")
-                return
-            _lib.check(_lib.lib.sb_grouped_swiglu(
-                p.rows.data_ptr(), p.tile_table.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
-                w.slot_of_expert.data_ptr(), p.slot_scale.data_ptr(), p.r_cap, w.hidden, w.inter, w.n_slots,
-                hbuf.data_ptr(), y.data_ptr(), self.status.data_ptr(), stream), "sb_grouped_swiglu")
-
+    def run_routed(self, needed: List[int], gemm, plan: Optional[EpipePlan]) -> None:
+        """Make the `needed` experts resident and call `gemm()` (a grouped launch
+        over the current slot map) on them: one launch when the cache holds them
+        all, several waves otherwise, in readiness order when `plan` says so."""
+        st, w = self.store, self.store.w
         protect = set(needed)
         self.launch_groups = 0
 
@@ -486,6 +446,53 @@ class CachedLayerRunner:
             else:
                 run_group([plan.residual] + plan.rest)    # a hit that waits for the prefetch event
         st.note_compute_done()
+
+    def forward(self, x: torch.Tensor, stage: str = "") -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        st, w, k = self.store, self.store.w, self.top_k
+        t = x.shape[0]
+        stage = stage or SparseContext.stage(1 if t == 1 else t)
+        idx, wts, logits, shared_scale = ops.router_topk(
+            x, w.router_w, k, bias=w.router_bias, w_shared_gate=w.shared_gate_w, renorm=self.renorm,
+            fp32_logits=self.fp32_logits)
+        p = ops.permute(x, idx.reshape(-1), w.num_experts, k, item_scale=wts.reshape(-1))
+        needed = self._needed_experts(p.expert_offsets)
+        self.last_needed = needed
+        plan = self._epipe_plan(needed, stage)
+        self.last_plan = plan
+        hbuf = torch.empty((p.r_cap, w.inter), dtype=torch.bfloat16, device=w.device)
+        y = torch.empty((p.r_cap, w.hidden), dtype=torch.bfloat16, device=w.device)
+
+        # Up to DECODE_MAX_TOKENS rows take the same weight-streaming kernels the
+        # resident layer uses at that size, so both stay bit-identical; the
+        # shared expert rides in the first of those launches.
+        decode = t <= DECODE_MAX_TOKENS
+        shared_h = shared_dec = None
+        if decode and w.shared_inter:
+            shared_h = torch.empty((t, w.shared_inter), dtype=torch.bfloat16, device=w.device)
+            shared_dec = torch.empty((t, w.hidden), dtype=torch.bfloat16, device=w.device)
+        shared_pending = [decode and bool(w.shared_inter)]
+
+        def gemm():
+            stream = torch.cuda.current_stream(w.device).cuda_stream
+            if decode:
+                with_shared = shared_pending[0]
+                shared_pending[0] = False
+                _lib.check(_lib.lib.sb_decode_experts(
+                    x.data_ptr(), p.item_of_slot.data_ptr(), k, p.tile_table.data_ptr(),
+                    w.slot_of_expert.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(), p.slot_scale.data_ptr(),
+                    w.hidden, w.inter, w.n_slots, hbuf.data_ptr(), y.data_ptr(),
+                    w.shared_w13.data_ptr() if with_shared else 0, w.shared_w2.data_ptr() if with_shared else 0,
+                    shared_scale.data_ptr() if with_shared and shared_scale is not None else 0,
+                    w.shared_inter if with_shared else 0, t,
+                    shared_h.data_ptr() if with_shared else 0, shared_dec.data_ptr() if with_shared else 0,
+                    self.status.data_ptr(), stream), "sb_decode_experts")
+                return
+            _lib.check(_lib.lib.sb_grouped_swiglu(
+                p.rows.data_ptr(), p.tile_table.data_ptr(), 0, w.w13.data_ptr(), w.w2.data_ptr(),
+                w.slot_of_expert.data_ptr(), p.slot_scale.data_ptr(), p.r_cap, w.hidden, w.inter, w.n_slots,
+                hbuf.data_ptr(), y.data_ptr(), self.status.data_ptr(), stream), "sb_grouped_swiglu")
+
+        self.run_routed(needed, gemm, plan)
         shared_out = None
         if decode and w.shared_inter:
             if shared_pending[0]:                         # no routed launch happened (cannot occur with top_k >= 1)

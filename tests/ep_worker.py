@@ -14,6 +14,61 @@ from sparse_b200.block import B200MoeBlock  # noqa: E402
 from sparse_b200.layer import LayerRunner, LayerWeights  # noqa: E402
 
 
+class _RankEnv:
+    def __init__(self, rank, world, dev):
+        self.rank, self.world, self.local_rank, self.device = rank, world, dev.index, dev
+
+
+def offloaded_case(rank, world, dev):
+    """The reference-style block with expert_offload="cpu" under EP: owned experts
+    in pinned host memory, 3 device slots per rank, rr and epipe settings.  Rows
+    must equal the all-resident EP block bit for bit."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_gpu_cache import _Inner
+    from sparse_b200.config import method_settings
+    from sparse_b200.context import Metrics, SparseContext
+    from sparse_b200.moe_block import DistributedSparseMoeBlock
+    shape = synth.TINY
+    w = synth.make_weights(shape, weight_seed=0, zipf_s=1.2)
+    SparseContext.initialize(1, num_experts=shape.num_experts)
+
+    def build(offload, cache, env_vars, metrics=None):
+        old = dict(os.environ)
+        os.environ.update(env_vars)
+        try:
+            return DistributedSparseMoeBlock(
+                layer_idx=0, mlp_block=_Inner(w).to(torch.bfloat16), scp_map={}, env=_RankEnv(rank, world, dev),
+                num_layers=1, num_experts=shape.num_experts, top_k=shape.top_k, dtype=torch.bfloat16,
+                expert_offload=offload, expert_cache=cache, routing_mode="router", rs_dir="",
+                rs_require_complete=False, rs_prob_to_logit_eps=1e-6, log_routing_stats=False, metrics=metrics,
+                planner_mode="none", prefetch_top_m=2, placement_mode="round_robin", max_tokens=256,
+                process_group=dist.group.WORLD)
+        finally:
+            os.environ.clear()
+            os.environ.update(old)
+
+    ref = build("gpu", 0, {})
+    for method in ("rr", "epipe"):
+        _, env_vars = method_settings(method, ep_size=world)
+        metrics = Metrics()
+        blk = build("cpu", 3, env_vars, metrics)
+        assert blk.store is not None and blk._ep is not None and blk.store.cache.capacity == 3
+        for step, tokens in enumerate((2, 2, 40, 2, 150, 1, 2)):
+            SparseContext.current_phase = "decode" if tokens <= 2 else "prefill"
+            SparseContext.begin_runtime_call(step)
+            x = synth.make_hidden(tokens, shape.hidden, seed=300 + 7 * step + rank).to(torch.bfloat16)
+            x = x.view(1, tokens, shape.hidden).to(dev) if tokens > 2 else x.view(tokens, 1, shape.hidden).to(dev)
+            want, want_logits = ref(x)
+            got, logits = blk(x)
+            torch.cuda.synchronize()
+            blk.check_status()
+            ref.check_status()
+            assert torch.equal(logits, want_logits)
+            assert torch.equal(got, want), "offloaded EP rows differ (method %s step %d rank %d)" % (method, step, rank)
+        assert metrics.cache_miss_count > 0 and len(blk.store.cache.resident_ids()) <= 3
+        dist.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -64,6 +119,7 @@ def main():
             blk.check_status()
             assert torch.equal(out_static, wants[it]), "graph-replayed EP rows differ on rank %d" % rank
         dist.barrier()
+    offloaded_case(rank, world, dev)
     print("EP_WORKER_OK rank %d" % rank, flush=True)
     dist.barrier()
     dist.destroy_process_group()
