@@ -261,10 +261,23 @@ def test_mixed_swiglu_few_rows_per_expert(bound):
             p.rows.data_ptr(), p.tile_table.data_ptr(), w13.data_ptr(), w2.data_ptr(), None,
             p.slot_scale.data_ptr(), r_cap, h, i, e, hbuf.data_ptr(), out.data_ptr(), bound,
             xs_d.data_ptr(), sw13.data_ptr(), sw2.data_ptr(), shs_d.data_ptr(), ish, t_sh,
-            sh_h.data_ptr(), sh_out.data_ptr(), status.data_ptr(),
+            sh_h.data_ptr(), sh_out.data_ptr(), None, status.data_ptr(),
             torch.cuda.current_stream(d).cuda_stream), "sb_grouped_swiglu_mixed")
+        # the same call with a destination address per row (the scatter used by the
+        # expert-parallel return path): row r lands in row perm[r] of another buffer
+        perm = torch.randperm(n)
+        ret = torch.zeros((n, h), dtype=bf, device=d)
+        dst = torch.zeros(r_cap, dtype=torch.int64)
+        dst[:n] = ret.data_ptr() + perm * (h * 2)
+        dst_d = dst.to(d)
+        _lib.check(_lib.lib.sb_grouped_swiglu_mixed(
+            p.rows.data_ptr(), p.tile_table.data_ptr(), w13.data_ptr(), w2.data_ptr(), None,
+            p.slot_scale.data_ptr(), r_cap, h, i, e, hbuf.data_ptr(), None, bound,
+            None, None, None, None, 0, 0, None, None, dst_d.data_ptr(), status.data_ptr(),
+            torch.cuda.current_stream(d).cuda_stream), "sb_grouped_swiglu_mixed(row_dst)")
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+    assert torch.equal(ret.cpu()[perm], out.cpu()[:n])
     want, _ = _oracle_grouped(x, p.expert_offsets.cpu(), gate, up, down, scale)
     got = out.cpu()[:n]
     assert rel_l2(got, want) < REL_L2
