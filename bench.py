@@ -330,6 +330,130 @@ def decode_stack(lw, shape, peaks, layers=24, counts=(1, 8, 16)):
     return out
 
 
+class _Lin:
+    """The two attributes of a linear layer that the block constructor reads."""
+    def __init__(self, weight, bias=None):
+        self.weight, self.bias = weight, bias
+
+
+class _Mlp:
+    def __init__(self, g, u, d):
+        self.gate_proj, self.up_proj, self.down_proj = _Lin(g), _Lin(u), _Lin(d)
+
+
+class _QwenLikeBlock:
+    """Duck-typed stand-in for the framework MoE block the reference wraps."""
+    def __init__(self, w):
+        self.gate = _Lin(w.router, w.router_bias)
+        self.experts = [_Mlp(w.gate[e], w.up[e], w.down[e]) for e in range(w.shape.num_experts)]
+        self.shared_expert = _Mlp(w.sh_gate, w.sh_up, w.sh_down)
+        self.shared_expert_gate = _Lin(w.sh_scalar_gate)
+        self.norm_topk_prob = w.shape.norm_topk_prob
+
+
+class _Env:
+    def __init__(self, dev):
+        self.rank, self.world, self.local_rank, self.device = 0, 1, dev.index or 0, dev
+
+
+def offload_methods(args):
+    """Opt-in (`--offload-methods`): decode steps (8 tokens) through a 4-layer
+    stack of reference-style blocks whose experts live in pinned host memory with
+    16 device slots per layer, under the reference's method switches (rr, epipe,
+    rs, rs-epipe), next to the all-resident stack.  The RS predictor is a
+    stand-in for a trained checkpoint: the next layer's own router applied to the
+    current layer's input."""
+    import gc
+    import torch.nn as nn
+    from sparse_b200 import synth
+    from sparse_b200.config import method_settings
+    from sparse_b200.context import Metrics, SparseContext
+    from sparse_b200.moe_block import DistributedSparseMoeBlock
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = synth.QWEN_MOE
+    w = synth.make_weights(shape, weight_seed=0, zipf_s=ZIPF_S)
+    src = _QwenLikeBlock(w)
+    layers, cache, tokens, steps, warm = 4, 16, 8, 48, 16
+
+    class NextRouterProbe(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.wt = w.router.to(torch.bfloat16).float().t().contiguous().to(dev)
+            self.b = w.router_bias.float().to(dev) if w.router_bias is not None else None
+
+        def forward(self, x):
+            z = x.float() @ self.wt
+            return torch.softmax(z + self.b if self.b is not None else z, dim=-1)
+
+    def build(method):
+        SparseContext.initialize(layers, num_experts=shape.num_experts)
+        metrics = Metrics()
+        old = dict(os.environ)
+        offload, planner = "gpu", "none"
+        if method != "resident":
+            flags, env = method_settings(method, ep_size=1)
+            env["SPARSE_RS_CACHE_SAFE_MIN_SCORE_BY_RANK"] = "0.0"
+            env["SPARSE_PREFETCH_MIN_CAND_SCORE"] = "0.0"
+            os.environ.update(env)
+            offload, planner = "cpu", flags["--planner-mode"]
+        try:
+            blocks = [DistributedSparseMoeBlock(
+                layer_idx=l, mlp_block=src, scp_map={}, env=_Env(dev), num_layers=layers,
+                num_experts=shape.num_experts, top_k=shape.top_k, dtype=torch.bfloat16, expert_offload=offload,
+                expert_cache=cache, routing_mode="router", rs_dir="", rs_require_complete=False,
+                rs_prob_to_logit_eps=1e-6, log_routing_stats=False, metrics=metrics, planner_mode=planner,
+                prefetch_top_m=2, placement_mode="round_robin", max_tokens=64) for l in range(layers)]
+        finally:
+            os.environ.clear()
+            os.environ.update(old)
+        for l, b in enumerate(blocks):
+            SparseContext.register_layer_block(l, b)
+        if planner == "rs_prefetch":
+            SparseContext.rs_bank = nn.ModuleList([NextRouterProbe() for _ in range(layers)])
+            SparseContext.rs_bank_source_layers = list(range(-1, layers - 1))
+        return blocks, metrics
+
+    out = {}
+    for method in ("resident", "rr", "epipe", "rs", "rs-epipe"):
+        blocks, metrics = build(method)
+        SparseContext.current_phase = "decode"
+        t_acc, h0, m0, b0 = 0.0, 0, 0, 0
+        for step in range(steps):
+            SparseContext.begin_runtime_call(step)
+            x = synth.make_hidden(tokens, shape.hidden, seed=5000 + step).to(torch.bfloat16).view(tokens, 1, -1).to(dev)
+            torch.cuda.synchronize()
+            if step == warm:
+                h0, m0, b0 = metrics.cache_hit_count, metrics.cache_miss_count, metrics.expert_weight_h2d_bytes
+            t0 = time.perf_counter()
+            for blk in blocks:
+                y, _ = blk(x)
+                x = (x + y).contiguous()
+            torch.cuda.synchronize()
+            if step >= warm:
+                t_acc += time.perf_counter() - t0
+        for blk in blocks:
+            blk.check_status()
+        n = steps - warm
+        hits, misses = metrics.cache_hit_count - h0, metrics.cache_miss_count - m0
+        out[method] = {"ms_per_step": t_acc / n * 1e3, "us_per_layer": t_acc / n / layers * 1e6,
+                       "tokens_per_s": tokens / (t_acc / n),
+                       "cache_hit_rate": hits / max(1, hits + misses),
+                       "h2d_mb_per_step": (metrics.expert_weight_h2d_bytes - b0) / n / 1e6,
+                       "prefetch_issued": metrics.prefetch_issued_count,
+                       "prefetch_used_before_demand": metrics.prefetch_complete_before_use_count,
+                       "epipe_triggered": metrics.epipe_trigger_count}
+        del blocks
+        gc.collect()
+        torch.cuda.empty_cache()
+    emit({"metric": "offloaded_decode_step", "config": {
+        "workload": "qwen1.5-moe-a2.7b-shaped MoE blocks, %d layers, %d tokens per decode step, experts in pinned "
+                    "host memory, %d device slots per layer, zipf(1.2) router bias" % (layers, tokens, cache),
+        "predictor": "stand-in: next layer's router applied to the current layer's input",
+        "timing": "host wall clock per step (the offloaded path synchronises once per layer), %d steps after "
+                  "%d warm-up steps" % (steps - warm, warm)}, "methods": out})
+
+
 def run_ours(args):
     from sparse_b200 import synth
     from sparse_b200.block import B200MoeBlock
@@ -609,7 +733,12 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode-to-prefill token sweep")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "rr"],
                     help="expert placement at N>1: load-balanced replicated (default) or round-robin")
+    ap.add_argument("--offload-methods", action="store_true",
+                    help="instead of the layer bench: decode steps with host-resident experts under rr/epipe/rs/rs-epipe")
     args = ap.parse_args()
+    if args.offload_methods:
+        offload_methods(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:
