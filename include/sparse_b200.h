@@ -196,6 +196,15 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
                           int32_t R_cap, int32_t H, int32_t I, int32_t S,
                           void *hbuf, void *out, int32_t *status, void *stream);
 
+/* sb_grouped_swiglu restricted to one of its two passes: `passes` 1 = gate/up +
+ * SwiGLU into `hbuf`, 2 = down projection from `hbuf` into `out`, 3 = both.
+ * Lets a caller put other work (a transfer on another stream) between the
+ * passes of the shared expert.  CTA-pair kernel only. */
+int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,
+                                 const void *w13, const void *w2, const int32_t *slot_of_expert,
+                                 const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
+                                 void *hbuf, void *out, int32_t passes, int32_t *status, void *stream);
+
 /* Token counts up to this use the weight-streaming kernels below inside
  * sb_moe_layer_forward instead of the tensor-core grouped GEMM. */
 #define SB_DECODE_MAX_TOKENS 16
@@ -396,6 +405,13 @@ int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *it
 int32_t sb_ep_resolve_return(const int32_t *recv_meta, const int32_t *recv_offsets, int32_t E,
                              void *const *peer_ret, int32_t ep, int32_t ret_rows, int32_t H, int32_t recv_cap,
                              uint64_t *row_dst, void *stream);
+/* The alternative to the fused scatter: after a plain sb_grouped_swiglu into the
+ * local output buffer `y` [recv_cap,H], copy every received row to its return
+ * address (whole rows, 512-byte warp stores).  Runs on a side stream beside the
+ * shared expert's down pass, which is how the return transfer is hidden when
+ * the fused store pattern would make the down GEMM NVLink-bound. */
+int32_t sb_ep_return_rows(const void *y, const uint64_t *row_dst, const int32_t *recv_offsets, int32_t E,
+                          int32_t H, int32_t recv_cap, void *stream);
 int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
                                   const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
                                   int32_t H, int32_t I, int32_t S, void *hbuf, const uint64_t *row_dst,

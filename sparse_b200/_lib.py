@@ -77,6 +77,8 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                              C.POINTER(vp), C.POINTER(vp), vp, vp, i32, C.POINTER(vp), vp]),
+    "sb_ep_return_rows": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "sb_grouped_swiglu_passes": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
     "sb_ep_resolve_return": (i32, [vp, vp, i32, C.POINTER(vp), i32, i32, i32, i32, vp, vp]),
     "sb_grouped_swiglu_scatter": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_combine": (i32, [C.POINTER(vp), vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),

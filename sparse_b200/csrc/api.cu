@@ -244,6 +244,17 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
                                shared_h, shared_out, status, 2, 0, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
+int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,
+                                 const void *w13, const void *w2, const int32_t *slot_of_expert,
+                                 const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
+                                 void *hbuf, void *out, int32_t passes, int32_t *status, void *stream) {
+  if (passes < 1 || passes > 3) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_passes: passes=%d", passes);
+  if (!sb_w13_interleaved())
+    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_passes: needs the CTA-pair kernel (SPARSE_B200_GEMM=pair)");
+  return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap, H, I,
+                                    S, hbuf, out, status, 0, 0, nullptr, static_cast<cudaStream_t>(stream), passes);
+}
+
 int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
                                   const int32_t *slot_of_expert, const void *row_scale, int32_t R_cap,
                                   int32_t H, int32_t I, int32_t S, void *hbuf, const uint64_t *row_dst,

@@ -292,6 +292,23 @@ ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs 
   }
 }
 
+// One warp per received row: the finished expert output row goes to the address
+// its sender asked for (a row of the sender's return buffer; a peer store when
+// the sender is another GPU).  512 contiguous bytes per warp store.
+__global__ void __launch_bounds__(256)
+ep_return_rows_kernel(const uint4 *__restrict__ y, const unsigned long long *__restrict__ row_dst,
+                      const int32_t *__restrict__ recv_offsets, int E, int vec_per_row) {
+  const int total = recv_offsets[E];
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * (blockDim.x >> 5);
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total; r += warps_total) {
+    uint4 *dst = reinterpret_cast<uint4 *>(row_dst[r]);
+    if (dst == nullptr) continue;
+    const uint4 *src = y + (size_t)r * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+  }
+}
+
 __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
   return pack_bf16x2(__fadd_rn(bf16_lo(a), bf16_lo(b)), __fadd_rn(bf16_hi(a), bf16_hi(b)));
 }
@@ -550,6 +567,20 @@ int32_t sb_ep_resolve_return(const int32_t *recv_meta, const int32_t *recv_offse
   ep_resolve_return_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       recv_meta, recv_offsets, E, pr, ep, ret_rows, (size_t)H * 2,
       reinterpret_cast<unsigned long long *>(row_dst));
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_return_rows(const void *y, const uint64_t *row_dst, const int32_t *recv_offsets, int32_t E,
+                          int32_t H, int32_t recv_cap, void *stream) {
+  if (!y || !row_dst || !recv_offsets || E < 1 || E > kMaxExperts || H <= 0 || H % 8 != 0 || recv_cap < 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_return_rows: bad arguments");
+  int blocks = (recv_cap + 7) / 8;
+  const int max_blocks = sb_device_sm_count() * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  if (blocks < 1) blocks = 1;
+  ep_return_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4 *>(y), reinterpret_cast<const unsigned long long *>(row_dst), recv_offsets, E, H / 8);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

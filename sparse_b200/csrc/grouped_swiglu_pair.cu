@@ -481,12 +481,13 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
 // `skip_rows_upto` rows are left to the caller (0 = none); `max_pairs` > 0
 // limits the grid to that many CTA pairs.  With `row_dst` (one device address per
 // row, 0 = drop) the down pass writes each result row to that address instead
-// of `out`.
+// of `out`.  `passes`: 1 = gate/up + SwiGLU only, 2 = down only (hbuf already
+// holds the intermediate rows), 3 = both.
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
                                    int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, int passes) {
   if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
     return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
   if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
@@ -508,9 +509,12 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   int grid = (sb_device_sm_count() / 2) * 2;
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
   if (max_pairs > 0 && 2 * max_pairs < grid) grid = 2 * max_pairs;     // leave the other SMs to a concurrent launch
-  rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
-                                H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stream);
-  if (rc != SB_OK) return rc;
+  if (passes & 1) {
+    rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
+                                  H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stream);
+    if (rc != SB_OK) return rc;
+  }
+  if (!(passes & 2)) return SB_OK;
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
                                  I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stream);
 }

@@ -109,7 +109,7 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
                                    const void *w13, const void *w2, const int32_t *slot_of_expert,
                                    const void *row_scale, int R_cap, int H, int I, int S,
                                    void *hbuf, void *out, int32_t *status, int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
-                                   cudaStream_t stream);
+                                   cudaStream_t stream, int passes = 3);
 int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int items_per_row,
                               const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,

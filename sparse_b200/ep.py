@@ -23,6 +23,8 @@ arithmetic is tested on a single GPU.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from typing import List, Optional, Sequence
 
@@ -323,10 +325,22 @@ class EpRank:
         self.launches += 1
         self._scattered = self.scatter_return
 
-    def stage_shared(self) -> None:
+    def stage_shared(self, passes: int = 3) -> None:
+        """The shared expert on this rank's own tokens; `passes` 1 / 2 run only its
+        gate/up or only its down pass (batches above the decode size)."""
         w, t = self.w, self._t
         if not w.shared_inter or t == 0:
             return
+        if passes != 3 and not self._small():
+            check(lib.sb_grouped_swiglu_passes(
+                self._x.data_ptr(), None, t, w.shared_w13.data_ptr(), w.shared_w2.data_ptr(), None,
+                self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, t, w.hidden,
+                w.shared_inter, 1, self.shared_h.data_ptr(), self.shared_out.data_ptr(), passes,
+                self.status.data_ptr(), self._s()), "sb_grouped_swiglu_passes(shared)")
+            self.launches += 1
+            return
+        if passes == 2 and self._small():
+            return                          # the decode-sized kernels did both passes in the first call
         if self._small():
             check(lib.sb_decode_experts(
                 self._x.data_ptr(), None, 1, None, None, None, None, None, w.hidden, w.inter, 1, None, None,
@@ -353,9 +367,21 @@ class EpRank:
                                        self.row_dst.data_ptr(), self._s()), "sb_ep_resolve_return")
         self.launches += 1
 
-    def stage_experts(self) -> None:
+    def stage_return(self) -> None:
+        """Push the finished rows of `y` to their senders (after stage_experts(fused=False))."""
+        if not self._scattered:
+            return
+        b = self.bufs
+        check(lib.sb_ep_return_rows(b.local["y"], self.row_dst.data_ptr(), self.recv_offsets.data_ptr(),
+                                    self.w.num_experts, self.w.hidden, b.recv_cap, self._s()), "sb_ep_return_rows")
+        self.launches += 1
+
+    def stage_experts(self, fused: bool = True) -> None:
+        """Routed experts over the received rows.  With return addresses
+        (`_scattered`) the rows go back to their senders either from the down GEMM's
+        own epilogue (`fused`) or, written to the local `y` first, by stage_return."""
         w, b = self.w, self.bufs
-        dst = self.row_dst.data_ptr() if self._scattered else None
+        dst = self.row_dst.data_ptr() if (self._scattered and fused) else None
         if self._small():
             # few rows per expert arrive in a decode step, whatever the peers sent
             check(lib.sb_grouped_swiglu_mixed(
@@ -365,7 +391,7 @@ class EpRank:
                 dst, self.status.data_ptr(), self._s()), "sb_grouped_swiglu_mixed(routed)")
             self.launches += 4
             return
-        if self._scattered:
+        if self._scattered and fused:
             check(lib.sb_grouped_swiglu_scatter(
                 b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
                 w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
@@ -420,10 +446,19 @@ class ExpertParallelLayer:
         self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits)
         self.last_launches = 0
         self.overlap = True
+        # How routed results travel back: "fused" = peer stores from the down GEMM's
+        # epilogue; "split" = whole-row pushes on the side stream beside the shared
+        # expert's down pass.  auto: fused on 2 GPUs (measured faster there), split above.
+        mode = os.environ.get("SPARSE_B200_EP_RETURN", "auto")
+        if mode not in ("auto", "fused", "split"):
+            raise ValueError("SPARSE_B200_EP_RETURN must be auto, fused or split")
+        self.return_mode = mode if mode != "auto" else ("fused" if ep <= 2 else "split")
         with torch.cuda.device(weights.device):
             self._side = torch.cuda.Stream(device=weights.device)
             self._fork = torch.cuda.Event()
             self._join = torch.cuda.Event()
+            self._fork2 = torch.cuda.Event()
+            self._join2 = torch.cuda.Event()
 
     @property
     def logits(self):
@@ -482,9 +517,10 @@ class ExpertParallelLayer:
                 self.last_launches = r.launches
                 return res
             else:
-                # The shared expert needs nothing from the peers: it runs on the
-                # caller's stream while count exchange, plan, dispatch and the
-                # "rows landed" barrier run beside it on the side stream.
+                # The shared expert needs nothing from the peers, so its two passes
+                # cover the two transfers: gate/up runs while counts, plan, dispatch
+                # and the "rows landed" barrier run on the side stream; down runs
+                # while the routed results travel back to their senders.
                 r.stage_route(x)
                 r.stage_publish()
                 self._fork.record(stream)
@@ -496,10 +532,28 @@ class ExpertParallelLayer:
                     self._barrier()
                     r.stage_resolve()
                     self._join.record(self._side)
-                r.stage_shared()
+                split = r._scattered and not r._small() and self.return_mode == "split"
+                r.stage_shared(1 if split else 3)
                 stream.wait_event(self._join)
-            r.stage_experts()
+                if split:
+                    r.stage_experts(fused=False)
+                    self._fork2.record(stream)
+                    with torch.cuda.stream(self._side):
+                        self._side.wait_event(self._fork2)
+                        r.stage_return()
+                        self._barrier()
+                        self._join2.record(self._side)
+                    r.stage_shared(2)
+                    stream.wait_event(self._join2)
+                    res = r.stage_combine(out)
+                    self.last_launches = r.launches
+                    return res
+            fused = marks is None          # the timing marks time the GEMM and the return push separately
+            r.stage_experts(fused=fused)
             mark("routed_swiglu")
+            if not fused:
+                r.stage_return()
+                mark("return rows")
             self._barrier()
             mark("barrier(outputs ready)")
             res = r.stage_combine(out)
