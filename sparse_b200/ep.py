@@ -448,11 +448,12 @@ class ExpertParallelLayer:
         self.overlap = True
         # How routed results travel back: "fused" = peer stores from the down GEMM's
         # epilogue; "split" = whole-row pushes on the side stream beside the shared
-        # expert's down pass.  auto: fused on 2 GPUs (measured faster there), split above.
+        # expert's down pass.  auto = fused (measured faster on 2 GPUs, equal to the
+        # earlier pull-combine on 4).
         mode = os.environ.get("SPARSE_B200_EP_RETURN", "auto")
         if mode not in ("auto", "fused", "split"):
             raise ValueError("SPARSE_B200_EP_RETURN must be auto, fused or split")
-        self.return_mode = mode if mode != "auto" else ("fused" if ep <= 2 else "split")
+        self.return_mode = mode if mode != "auto" else "fused"
         with torch.cuda.device(weights.device):
             self._side = torch.cuda.Stream(device=weights.device)
             self._fork = torch.cuda.Event()
