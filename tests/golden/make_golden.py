@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of louislichen/SPARSE>
 
 It imports the reference's `utils.eval_core`, wraps a stand-in inner MoE block
 (the attribute layout of transformers 4.44: `gate`, `experts` ModuleList of
@@ -149,7 +149,7 @@ CASES = [
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)

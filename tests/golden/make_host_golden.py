@@ -1,6 +1,6 @@
 """Golden traces for the host-side logic, produced by running the REFERENCE:
 
-    python tests/golden/make_host_golden.py --reference /root/reference
+    python tests/golden/make_host_golden.py --reference <checkout of louislichen/SPARSE>
 
 Writes tests/golden/host_golden.json with
   * random operation sequences on the reference's `ExpertWeightCache` and what
@@ -134,7 +134,7 @@ def placement_cases(ec):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     for k in list(os.environ):

@@ -3,7 +3,7 @@ methods (`_build_target_layer_prob_score_map`, `_build_prefetch_plan_from_score_
 `_pick_victims_by_low_value` of DistributedSparseMoeBlock) bound to a small
 stand-in object, in the manner of the reference's AST-extraction unit tests.
 
-    python tests/golden/make_planner_golden.py --reference /root/reference
+    python tests/golden/make_planner_golden.py --reference <checkout of louislichen/SPARSE>
 """
 import argparse
 import json
@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     for k in list(os.environ):
