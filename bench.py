@@ -676,18 +676,18 @@ def run_ours(args):
             "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
         }
         # whole-layer roofline per GPU: slower of dense compute at peak and
-        # (HBM bytes at HBM peak + NVLink bytes at 900 GB/s per direction)
+        # (HBM bytes at HBM peak + NVLink bytes at the measured 770 GB/s per direction)
         layer_flops = shape.flops_per_token() * t
         hbm_bytes = distinct * shape.routed_expert_bytes_bf16 + 3 * shape.hidden * shape.shared_inter * 2 \
             + 2 * t * shape.hidden * 2
         nvlink_bytes = 0 if world == 1 else t * shape.top_k * (world - 1) / world * shape.hidden * 2
-        t_mem = hbm_bytes / (peaks["hbm_gbs"] * 1e9) + 2 * nvlink_bytes / 900e9
+        t_mem = hbm_bytes / (peaks["hbm_gbs"] * 1e9) + 2 * nvlink_bytes / 770e9
         t_roof = max(layer_flops / (peaks["bf16_tflops"] * 1e12), t_mem)
         line["layer_roofline"] = {"roofline_ms": t_roof * 1e3, "measured_ms": ms_dev / args.steps,
                                   "frac": t_roof * 1e3 / (ms_dev / args.steps),
                                   "distinct_experts": distinct,
                                   "nvlink_bytes_per_gpu_per_direction": nvlink_bytes,
-                                  "nvlink_peak": "900 GB/s per direction (datasheet)"}
+                                  "nvlink_peak": "770 GB/s per direction (measured peer copy on this pool; 900 nominal)"}
         if decode:
             line["decode"] = decode
         if world == 1 and not args.no_sweep:
