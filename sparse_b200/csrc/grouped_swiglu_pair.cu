@@ -54,7 +54,8 @@ constexpr uint32_t kLightTokBytes = 16 * kBlockK * 2;         // 2 KB: a 16-row 
 // the bytes in flight, which is what bounds a tile that is pure weight traffic.
 constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kLightTokBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr uint32_t kScatterTileBytes = 16 * kRowsPerCta * 2;    // 16 tokens x this CTA's 128 output columns, bf16
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * kScatterTileBytes;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kSlotSkip = -2;
 constexpr int kModeSwiglu = 0, kModeScale = 1;
@@ -376,15 +377,33 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           } else {
             // Scatter: every row goes straight to the address its sender asked for
             // (a row of the sender's return buffer, possibly on another GPU), so
-            // the transfer back overlaps the GEMM instead of following it.
+            // the transfer back overlaps the GEMM instead of following it.  The four
+            // warps that share this token chunk first put their 32-column pieces
+            // side by side in shared memory, so that what leaves the SM are
+            // 256-byte row segments, not 64-byte ones.
             unsigned long long my_dst = 0ull;
             if (c0 + lane < n_tok) my_dst = row_dst[ch.tok_begin + c0 + lane];
+            __nv_bfloat16 *stg = reinterpret_cast<__nv_bfloat16 *>(
+                smem_al + kStages * kStageBytes + 256 + half * kScatterTileBytes);
+            const int col0 = wt * kTileW + (int)cta * kRowsPerCta;       // first output column of this CTA
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float sc = __shfl_sync(0xffffffffu, my_scale, j);
-              const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, j);
-              const float y = round_bf16(__uint_as_float(v[j])) * sc;
-              if (col_ok && d != 0ull) reinterpret_cast<__nv_bfloat16 *>(d)[wrow] = __float2bfloat16_rn(y);
+            for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float sc = __shfl_sync(0xffffffffu, my_scale, sub * 16 + j);
+                const float y = round_bf16(__uint_as_float(v[sub * 16 + j])) * sc;
+                stg[j * kRowsPerCta + wl] = __float2bfloat16_rn(y);
+              }
+              asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int tj = lane_group * 4 + q;
+                const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, sub * 16 + tj);
+                const uint2 piece = *reinterpret_cast<const uint2 *>(stg + tj * kRowsPerCta + lane * 4);
+                if (d != 0ull && col0 + lane * 4 + 3 < ld_out)
+                  *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(d) + col0 + lane * 4) = piece;
+              }
+              asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
             }
           }
         }
