@@ -1,19 +1,23 @@
 """Expert-parallel layer pass: tokens sharded by rank, experts sharded by owner,
 rows moved by this library's own kernels over NVLink peer memory.
 
-One process per GPU.  Each rank allocates four exportable buffers (receive
-rows, receive route weights, expert outputs, counts + flags), exchanges their
-CUDA IPC handles once through `torch.distributed` (the only use of the process
-group on this path), and from then on a layer pass is a fixed sequence of
-kernel launches on one stream with no host synchronisation:
+One process per GPU.  Each rank allocates six exportable buffers (receive rows,
+receive route weights, return addresses of the received rows, expert outputs,
+the return buffer its own results come back into, counts + flags), exchanges
+their CUDA IPC handles once through `torch.distributed` (the only use of the
+process group on this path), and from then on a layer pass is a fixed sequence
+of kernel launches with no host synchronisation:
 
-    router -> local sort -> publish counts -> barrier -> plan -> dispatch
-           -> shared expert (overlaps the peers' dispatch) -> barrier
-           -> grouped SwiGLU on the received rows -> barrier -> combine
+    router -> local sort -> publish counts -> barrier -> plan -> dispatch (rows,
+    weights, return addresses) -> barrier -> resolve return addresses
+           -> grouped SwiGLU on the received rows, result rows stored straight
+              into the senders' return buffers -> barrier -> local combine
 
-The receive buffers are reused by every layer; the barriers order the reuse
-(a rank cannot start writing into a peer's buffer for the next pass before
-that peer has passed the previous pass's last barrier).
+The shared expert runs on the caller's stream beside the exchange (side stream);
+decode-sized steps use a shorter single-stream sequence with fused launches.
+The buffers are reused by every layer; the barriers order the reuse (a rank
+cannot start writing into a peer's buffer for the next pass before that peer
+has passed the previous pass's last barrier).
 
 `EpRank.stage_*` are the individual steps; `ExpertParallelLayer.forward` strings
 them together with barriers.  The stages can also be driven for several
