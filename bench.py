@@ -45,8 +45,8 @@ N_INPUT_BATCHES = 4          # rotated so a step never re-reads the previous ste
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel
 # (pair_gemm_kernel), averaged over the four launches of one step (routed
 # gate/up 737.3 MB, routed down 412.5 MB, shared gate/up 106.6 MB, shared down
-# 73.6 MB = 1330.0 MB per step), from the ncu capture summarised in
-# profiles/pair_gemm_qwen_t4096.md.  The algorithmic bytes of the same four
+# 73.6 MB = 1330.0 MB per step), from one `ncu --set full` capture of this
+# workload on a B200 (2026-11-25).  The algorithmic bytes of the same four
 # launches are 1355.8 MB: nothing is re-read from DRAM.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 332502144
 
@@ -155,15 +155,16 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = min(max(1, args.steps), 20)
-    warmup = min(max(1, args.warmup), 3)
+    steps = max(1, args.steps)
+    warmup = max(3, args.warmup)
     tps, ms, cores = cpu_reference_tokens_per_s(steps, warmup)
-    sample = "first %d of the %d tokens, fp32, %d steps" % (CPU_SAMPLE_TOKENS, TOKENS_PER_GPU, steps)
+    sample = ("each step = the first %d of the %d tokens of a batch, fp32, all host threads; "
+              "%d steps after %d warm-up steps" % (CPU_SAMPLE_TOKENS, TOKENS_PER_GPU, steps, warmup))
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "data": "synthetic", "config": workload_config(max(1, args.gpus), "n/a (host cores)"),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -172,7 +173,103 @@ def run_reference_arm(args):
     emit(line)
 
 
+def workload_config(world, placement_note):
+    """The `config` object of the JSON line (both arms print the same one)."""
+    from sparse_b200 import synth
+    shape = synth.QWEN_MOE
+    return {"workload": WORKLOAD, "tokens_per_gpu": TOKENS_PER_GPU, "experts": shape.num_experts,
+            "top_k": shape.top_k, "hidden": shape.hidden, "inter": shape.inter,
+            "shared_inter": shape.shared_inter,
+            "parallelism": "ep%d" % world if world > 1 else "ep1",
+            "placement": placement_note,
+            "l2": "weights 1.1 GB per layer exceed the 126 MB L2; %d input batches rotated" % N_INPUT_BATCHES}
+
+
 # ------------------------------------------------------------------ GPU arm ----
+
+def _time_steps(fn, steps, stream):
+    """Like _time_region, with an event after every step: (total ms, per-step ms list)."""
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record(stream)
+    for i in range(steps):
+        fn(i)
+        evs[i + 1].record(stream)
+    evs[-1].synchronize()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return evs[0].elapsed_time(evs[-1]), per
+
+
+def _step_stats(per):
+    s = sorted(per)
+    n = len(s)
+    head = per[:min(10, n)]
+    return {"min": s[0], "median": s[n // 2], "p90": s[min(n - 1, int(0.9 * n))], "max": s[-1],
+            "first_10_mean": sum(head) / len(head)}
+
+
+def torch_eager_tokens_per_s(w, shape, x, steps=5):
+    """The reference block's own op sequence (library GEMMs: F.linear per expert,
+    softmax, torch.topk, index_add_ in ascending expert order;
+    utils/eval_core.py:9519-9595, 14690-14721, 9455-9463 of the reference) run
+    eagerly on this GPU in bf16: the cuBLAS/ATen bar the hand-written kernels
+    have to beat on the same box.  Not used for any parity claim."""
+    import torch.nn.functional as F
+    dev = x.device
+    bf = torch.bfloat16
+    router = w.router.to(bf).to(dev)
+    rbias = None if w.router_bias is None else w.router_bias.to(bf).to(dev)
+    gate = [g.to(bf).to(dev) for g in w.gate]
+    up = [u.to(bf).to(dev) for u in w.up]
+    down = [d.to(bf).to(dev) for d in w.down]
+    sg, su, sd = w.sh_gate.to(bf).to(dev), w.sh_up.to(bf).to(dev), w.sh_down.to(bf).to(dev)
+    ssg = w.sh_scalar_gate.to(bf).to(dev)
+
+    def forward(xx):
+        logits = F.linear(xx, router, rbias)
+        probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
+        topv, topi = torch.topk(probs, shape.top_k, dim=-1)
+        topv = topv.to(xx.dtype)
+        out = torch.zeros_like(xx)
+        mask = F.one_hot(topi, num_classes=shape.num_experts).permute(2, 1, 0)
+        for e in range(shape.num_experts):
+            idx_k, top_x = torch.where(mask[e])
+            if top_x.numel() == 0:
+                continue
+            cur = xx[top_x]
+            y = F.linear(F.silu(F.linear(cur, gate[e])) * F.linear(cur, up[e]), down[e])
+            out.index_add_(0, top_x, y * topv[top_x, idx_k, None])
+        sh = F.linear(F.silu(F.linear(xx, sg)) * F.linear(xx, su), sd)
+        return out + torch.sigmoid(F.linear(xx, ssg)) * sh
+
+    with torch.no_grad():
+        for _ in range(2):
+            forward(x)
+        torch.cuda.synchronize()
+        ms = _time_region(lambda i: forward(x), steps, torch.cuda.current_stream(dev)) / steps
+    return x.shape[0] / (ms * 1e-3), ms
+
+
+def routing_parity_rates(w, shape, x):
+    """How the kernel's routing compares with the reference's own calls on this
+    device (softmax in fp32 + torch.topk on CUDA, utils/eval_core.py:9591-9595):
+    from the kernel's logits, and from the library GEMM's logits."""
+    from sparse_b200 import ops
+    import torch.nn.functional as F
+    dev = x.device
+    wg = w.router.to(torch.bfloat16).to(dev)
+    bias = None if w.router_bias is None else w.router_bias.to(torch.bfloat16).to(dev)
+    idx, _, logits, _ = ops.router_topk(x, wg, shape.top_k, bias=bias)
+    ours = idx.long().sort(dim=1).values
+    _, ti = torch.topk(torch.softmax(logits, dim=-1, dtype=torch.float32), shape.top_k, dim=-1)
+    lib_logits = F.linear(x, wg, bias)
+    _, tl = torch.topk(torch.softmax(lib_logits, dim=-1, dtype=torch.float32), shape.top_k, dim=-1)
+    return {
+        "rows": int(x.shape[0]),
+        "set_match_torch_topk_cuda_same_logits": float((ti.sort(dim=1).values == ours).all(dim=1).float().mean()),
+        "ordered_match_torch_topk_cuda_same_logits": float((ti == idx.long()).all(dim=1).float().mean()),
+        "set_match_vs_library_gemm_logits": float((tl.sort(dim=1).values == ours).all(dim=1).float().mean()),
+        "logits_equal_to_library_gemm": float((lib_logits == logits).float().mean()),
+    }
 
 def _time_region(fn, steps, stream):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -477,28 +574,43 @@ def run_ours(args):
     shape = synth.QWEN_MOE
     t = TOKENS_PER_GPU
     w = synth.make_weights(shape, weight_seed=0, zipf_s=ZIPF_S)
-    placement = None
-    placement_note = "single GPU"
-    if world > 1 and args.placement == "balanced":
-        # Profile -> placement, as the reference's offline solver does for its
-        # replicated placements: expert load of a seeded calibration batch
-        # (not a bench input), hot experts replicated, sources spread over replicas.
-        from sparse_b200 import ops
-        from sparse_b200.placement import Placement, balanced_replicated_placement
-        xc = synth.make_hidden(4096, shape.hidden, seed=424242).to(torch.bfloat16).to(dev)
-        idx_c, _, _, _ = ops.router_topk(xc, w.router.to(torch.bfloat16).to(dev), shape.top_k,
-                                         bias=None if w.router_bias is None else w.router_bias.float().to(dev))
-        load = torch.bincount(idx_c.reshape(-1).long().cpu(), minlength=shape.num_experts).tolist()
-        obj = balanced_replicated_placement([load], world)
-        placement = Placement("scp_ep", 1, shape.num_experts, world, obj=obj, apply_decode=True)
-        held = [len(placement.receive_experts(0, r, "prefill")) for r in range(world)]
-        placement_note = ("load-balanced replicated placement from a calibration batch's expert histogram; "
-                          "experts held per rank %s" % held)
-    elif world > 1:
-        placement_note = "round-robin ownership (e %% %d)" % world
-    block = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=t,
-                                            process_group=None if world == 1 else dist.group.WORLD,
-                                            placement=placement)
+
+    def make_block(kind):
+        """kind: balanced | rr | perm:<seed>  ->  (block, note)"""
+        from sparse_b200.placement import Placement
+        placement, note = None, "single GPU"
+        if world > 1 and kind == "balanced":
+            # Profile -> placement, as the reference's offline solver does for its
+            # replicated placements: expert load of a seeded calibration batch
+            # (not a bench input), hot experts replicated, sources spread over replicas.
+            from sparse_b200 import ops
+            from sparse_b200.placement import balanced_replicated_placement
+            xc = synth.make_hidden(4096, shape.hidden, seed=424242).to(torch.bfloat16).to(dev)
+            idx_c, _, _, _ = ops.router_topk(xc, w.router.to(torch.bfloat16).to(dev), shape.top_k,
+                                             bias=None if w.router_bias is None else w.router_bias.float().to(dev))
+            load = torch.bincount(idx_c.reshape(-1).long().cpu(), minlength=shape.num_experts).tolist()
+            obj = balanced_replicated_placement([load], world)
+            placement = Placement("scp_ep", 1, shape.num_experts, world, obj=obj, apply_decode=True)
+            held = [len(placement.receive_experts(0, r, "prefill")) for r in range(world)]
+            note = ("load-balanced replicated placement from a calibration batch's expert histogram; "
+                    "experts held per rank %s" % held)
+        elif world > 1 and kind.startswith("perm:"):
+            # a seeded random permutation of the experts dealt round-robin, in the
+            # non-replicated placement schema {"placement": {layer: {expert: rank}}}
+            seed = int(kind.split(":", 1)[1])
+            g = torch.Generator().manual_seed(seed)
+            order = torch.randperm(shape.num_experts, generator=g).tolist()
+            obj = {"placement": {"0": {str(e): pos % world for pos, e in enumerate(order)}}}
+            placement = Placement("scp_ep", 1, shape.num_experts, world, obj=obj, apply_decode=True)
+            note = "seeded random-permutation ownership (seed %d), one owner per expert" % seed
+        elif world > 1:
+            note = "round-robin ownership (e %% %d)" % world
+        blk = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=t,
+                                              process_group=None if world == 1 else dist.group.WORLD,
+                                              placement=placement, use_graphs=True)
+        return blk, note
+
+    block, placement_note = make_block(args.placement)
     xs_host = [synth.make_hidden(t, shape.hidden, seed=1 + 97 * rank + b).to(torch.bfloat16).pin_memory()
                for b in range(N_INPUT_BATCHES)]
     xs = [xh.to(dev) for xh in xs_host]
@@ -519,19 +631,25 @@ def run_ours(args):
         return float(v.item())
 
     # ---- device-resident throughput ----
-    def step_dev(i):
-        block.forward_device(xs[i % N_INPUT_BATCHES])
+    # Every step is one graph launch: the step's kernels (two streams, device-side
+    # barrier epochs at N>1) were recorded once per input buffer during warm-up.
+    def step_dev(i, blk=None):
+        (blk or block).forward_device(xs[i % N_INPUT_BATCHES])
 
-    for i in range(max(3, args.warmup)):
-        step_dev(i)
-    barrier()
+    def timed_run(blk, steps, warmup):
+        # warm-up: one un-recorded pass, then one recording (and replay) per input buffer
+        for i in range(max(N_INPUT_BATCHES + 1, warmup)):
+            step_dev(i, blk)
+        barrier()
+        total, per = _time_steps(lambda i: step_dev(i, blk), steps, stream)
+        barrier()
+        blk.check_status()
+        return max_over_ranks(total), per
+
     sampler = ClockSampler(_physical_gpu_index(local_rank))
     sampler.start()
-    ms_dev = _time_region(step_dev, args.steps, stream)
-    barrier()
-    ms_dev = max_over_ranks(ms_dev)
+    ms_dev, per_step = timed_run(block, args.steps, args.warmup)
     launches = block.last_launches * args.steps
-    block.check_status()
 
     # ---- end to end through the host-buffer API ----
     # Every step copies ITS input batch from pinned host memory and ITS result
@@ -562,26 +680,87 @@ def run_ours(args):
     sampler.stop()
     barrier()
 
+    # ---- the copies alone: what the host link allows with every rank copying at once ----
+    # Same pinned buffers, same three streams' worth of overlap, no layer in between.
+    cp_in, cp_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    x_cp = [torch.empty_like(xs[0]) for _ in range(3)]
+
+    def copy_only(n):
+        for i in range(n):
+            with torch.cuda.stream(cp_in):
+                x_cp[i % 3].copy_(xs_host[i % N_INPUT_BATCHES], non_blocking=True)
+            with torch.cuda.stream(cp_out):
+                outs_host[i % 3].copy_(xs[i % N_INPUT_BATCHES], non_blocking=True)
+        cp_in.synchronize()
+        cp_out.synchronize()
+
+    copy_only(3)
+    barrier()
+    t0 = time.perf_counter()
+    copy_only(args.steps)
+    ms_copy = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    barrier()
+
+    # ---- N > 1: one untimed step checked bit for bit against the single-GPU layer ----
+    ep_parity = None
+    if world > 1:
+        ref_runner = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, t)
+        ok = 1
+        for b in range(2):
+            got = block.forward_device(xs[b]).clone()
+            want, want_idx, _, _ = ref_runner.forward(xs[b])
+            torch.cuda.synchronize()
+            idx_b, _ = block.topk(t)
+            if not (torch.equal(got, want) and torch.equal(idx_b, want_idx)):
+                ok = 0
+        block.check_status()
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ep_parity = {"ok": bool(int(flag.item())), "placement": args.placement,
+                     "check": "2 batches per rank: output rows and expert indices of the EP step equal to the "
+                              "single-GPU layer holding all 60 experts, torch.equal on every rank"}
+        barrier()
+
+    # ---- N > 1: the reference's own placements beside the default one ----
+    other_placements = {}
+    if world > 1 and not args.no_sweep:
+        for kind in ("rr", "perm:2", "balanced"):
+            if kind == args.placement:
+                continue
+            blk2, note2 = make_block(kind)
+            n2 = max(10, min(args.steps, 50))
+            ms2, per2 = timed_run(blk2, n2, N_INPUT_BATCHES + 1)
+            got = blk2.forward_device(xs[0]).clone()
+            want, _, _, _ = ref_runner.forward(xs[0])
+            torch.cuda.synchronize()
+            flag = torch.tensor([1 if torch.equal(got, want) else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            other_placements[kind] = {"ms_per_step": ms2 / n2, "tokens_per_s": t * world * n2 / (ms2 * 1e-3),
+                                      "steps": n2, "step_ms": _step_stats(per2), "placement": note2,
+                                      "ep_parity_ok": bool(int(flag.item()))}
+            del blk2
+            barrier()
+
     total_tokens = t * world * args.steps
     value = total_tokens / (ms_dev * 1e-3)
     e2e_value = total_tokens / (ms_e2e * 1e-3)
 
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_dev / args.steps,
+        "steps": args.steps, "warmup": max(N_INPUT_BATCHES + 1, args.warmup), "ms_per_step": ms_dev / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens_per_gpu": t, "experts": shape.num_experts,
-                   "top_k": shape.top_k, "hidden": shape.hidden, "inter": shape.inter,
-                   "shared_inter": shape.shared_inter,
-                   "parallelism": "ep%d" % world if world > 1 else "ep1",
-                   "placement": placement_note,
-                   "l2": "weights 1.1 GB per layer exceed the 126 MB L2; %d input batches rotated" % N_INPUT_BATCHES},
+        "config": workload_config(world, placement_note),
+        "step_ms": _step_stats(per_step),
+        "launch_mode": "each step replayed from a CUDA graph recorded during warm-up (one per input buffer)",
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": t * shape.hidden * 2 * world,
                 "d2h_bytes_per_step": t * shape.hidden * 2 * world,
                 "timing": "host wall clock from the first submit to the last result in pinned host memory, max over ranks",
                 "pipeline": "3 slots: copy-in, layer and copy-out of neighbouring steps overlap",
-                "single_batch_latency_ms": ms_e2e_sync},
+                "single_batch_latency_ms": ms_e2e_sync,
+                "copy_only_bound": {"value": total_tokens / (ms_copy * 1e-3), "unit": "tokens/s",
+                                    "what": "the same host->device and device->host copies of every step, all ranks "
+                                            "at once, no layer: what the host links allow"}},
         "gpu_launches": launches,
         "clocks": sampler.summary(),
     }
@@ -591,6 +770,7 @@ def run_ours(args):
     if world > 1:
         ep_layer = block._ep
         reps = max(3, min(args.steps, 20))
+        block.use_graphs = False              # the timing marks need the stage-by-stage path
         ep_layer.stage_events = []
         for i in range(reps):
             step_dev(i)
@@ -598,9 +778,25 @@ def run_ours(args):
         ep_marks = ep_layer.stage_events
         ep_layer.stage_events = None
         recv_rows = int(ep_layer.r.recv_offsets[-1].item())
+        # rows every rank received in that step, and its routed-GEMM time: the skew the barriers wait for
+        rows_all = torch.zeros(world, dtype=torch.int64, device=dev)
+        rows_all[rank] = recv_rows
+        dist.all_reduce(rows_all)
+        per = len(ep_marks) // reps
+        my_gemm = 0.0
+        for rep in range(reps):
+            chunk = ep_marks[rep * per:(rep + 1) * per]
+            for (n0, e0), (n1, e1) in zip(chunk[:-1], chunk[1:]):
+                if n1 == "routed_swiglu":
+                    my_gemm += e0.elapsed_time(e1) / reps
+        gemm_all = torch.zeros(world, dtype=torch.float64, device=dev)
+        gemm_all[rank] = my_gemm
+        dist.all_reduce(gemm_all)
+        rank_skew = {"received_rows": rows_all.tolist(), "routed_gemm_ms": [round(v, 4) for v in gemm_all.tolist()]}
 
     # ---- decode-sized steps through the same block (all ranks) ----
     decode = {}
+    block.use_graphs = False                  # the decode section times eager launches and its own graphs
     if not args.no_sweep:
         for td in (1, 8, 16):
             xd = [synth.make_hidden(td, shape.hidden, seed=900 + 31 * rank + b).to(torch.bfloat16).to(dev)
@@ -687,12 +883,28 @@ def run_ours(args):
                                   "frac": t_roof * 1e3 / (ms_dev / args.steps),
                                   "distinct_experts": distinct,
                                   "nvlink_bytes_per_gpu_per_direction": nvlink_bytes,
-                                  "nvlink_peak": "770 GB/s per direction (measured peer copy on this pool; 900 nominal)"}
+                                  "nvlink_peak": "770 GB/s per direction (measured peer copy on this pool); with the "
+                                                 "nominal 900 GB/s the bound moves by less than the flops term",
+                                  "roofline_ms_at_900": max(layer_flops / (peaks["bf16_tflops"] * 1e12),
+                                                            hbm_bytes / (peaks["hbm_gbs"] * 1e9)
+                                                            + 2 * nvlink_bytes / 900e9) * 1e3}
+        if ep_parity is not None:
+            line["ep_parity"] = ep_parity
+            line["rank_skew"] = rank_skew
+        if other_placements:
+            line["placements"] = other_placements
         if decode:
             line["decode"] = decode
         if world == 1 and not args.no_sweep:
             line["sweep"] = token_sweep(block.weights, shape, peaks)
             line["decode_stack"] = decode_stack(block.weights, shape, peaks)
+        if world == 1:
+            line["parity"] = routing_parity_rates(w, shape, xs[0])
+            if not args.no_sweep:
+                tps_e, ms_e = torch_eager_tokens_per_s(w, shape, xs[0])
+                line["torch_eager_gpu"] = {"value": tps_e, "unit": "tokens/s", "ms_per_step": ms_e,
+                                           "what": "the reference block's op sequence (per-expert F.linear on cuBLAS, "
+                                                   "torch.topk, index_add_) run eagerly on this GPU, same 4096 tokens"}
         if world == 1 and not args.no_cpu_baseline:
             tps, ms, cores = cpu_reference_tokens_per_s(3, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
@@ -731,11 +943,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the decode-to-prefill token sweep")
-    ap.add_argument("--placement", default="balanced", choices=["balanced", "rr"],
-                    help="expert placement at N>1: load-balanced replicated (default) or round-robin")
+    ap.add_argument("--placement", default="balanced",
+                    help="expert placement at N>1: balanced (load-balanced replicated, default), rr "
+                         "(round-robin) or perm:<seed> (seeded random permutation, one owner per expert)")
     ap.add_argument("--offload-methods", action="store_true",
                     help="instead of the layer bench: decode steps with host-resident experts under rr/epipe/rs/rs-epipe")
     args = ap.parse_args()
+    import re
+    if args.placement not in ("balanced", "rr") and not re.fullmatch(r"perm:\d+", args.placement):
+        ap.error("--placement must be balanced, rr or perm:<seed>")
     if args.offload_methods:
         offload_methods(args)
         return

@@ -58,12 +58,32 @@ const char *sb_last_error_string(void);
 /* Number of SMs of the current device (grid sizing on the host side). */
 int32_t sb_device_sm_count(void);
 
-/* Rows per tile of the tile tables this library writes and consumes (128 with
- * the single-CTA grouped GEMM, 256 with the CTA-pair kernel), and whether the
- * gate/up slab `w13` is expected with gate and up rows interleaved
- * (row 2j = gate_j, row 2j+1 = up_j) instead of stacked (I gate rows, then I
- * up rows).  Both follow the kernel choice made once per process through the
- * environment variable SPARSE_B200_GEMM (pair | single). */
+/* Once per device, before the first sb_moe_layer_forward on it: creates the
+ * layer driver's side stream and events for `device` (the only resources the
+ * library owns; they live until the process exits).  Idempotent and
+ * thread-safe; no entry point creates them lazily.  The reference has no
+ * counterpart: its block creates its prefetch and EPIPE streams in __init__
+ * (utils/eval_core.py:4939-4968). */
+int32_t sb_init(int32_t device);
+
+/* Process-wide scheduling knobs of the kernels, read at every launch; results
+ * are bit-identical under every setting, only the time changes.
+ *   "sched"          0 = walk the tile table in order with a fixed stride,
+ *                    1 = rank the row chunks by size and deal them out
+ *                        boustrophedon (default), 2 = as 1 with odd CTA pairs
+ *                        walking their list backwards
+ *   "dense_group"    row chunks per raster block of a dense (shared-expert)
+ *                    pass, 1..64 (default 1)
+ *   "router_overlap" 1 = sb_moe_layer_forward runs the router beside the shared
+ *                    expert's gate/up pass (default), 0 = in front of it
+ * Unknown keys and out-of-range values are SB_E_INVALID_ARG.  No counterpart in
+ * the reference (its knobs are environment variables read by the block). */
+int32_t sb_set_tuning(const char *key, int32_t value);
+
+/* Rows per tile of the tile tables this library writes and consumes (256: the
+ * token extent of one tensor-core tile of a CTA pair), and whether the gate/up
+ * slab `w13` is expected with gate and up rows interleaved (row 2j = gate_j,
+ * row 2j+1 = up_j; always 1) instead of stacked (I gate rows, then I up rows). */
 int32_t sb_tile_rows(void);
 int32_t sb_w13_interleaved(void);
 
@@ -178,12 +198,15 @@ int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
  *   rows          [R_cap,H] bf16, expert-sorted (out_rows of sb_permute)
  *   tile_table    as written by sb_permute; NULL = one dense group of
  *                 `dense_rows` rows using weight slot 0 (shared expert)
- *   w13           [S, 2*I, H] bf16 weight slab: per slot gate rows then up rows
+ *   w13           [S, 2*I, H] bf16 weight slab, per slot gate and up rows
+ *                 interleaved (row 2j = gate_j, row 2j+1 = up_j)
  *   w2            [S, H, I]   bf16 weight slab
  *   slot_of_expert[E] int32 expert id -> weight slot, or NULL for identity;
  *                 -2 = skip this expert's tiles in this launch (they are left
  *                 for a later launch, e.g. once its weights have arrived);
- *                 any other negative value is an error (status = 2)
+ *                 any other negative value, or one >= S, raises status 2
+ *                 and the expert's rows are left uncomputed (never run
+ *                 with another expert's weights)
  *   row_scale     [R_cap] bf16 per-row factor, or NULL for none
  *   hbuf          [R_cap, I] bf16 scratch for the intermediate
  *   out           [R_cap, H] bf16
@@ -199,11 +222,15 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
 /* sb_grouped_swiglu restricted to one of its two passes: `passes` 1 = gate/up +
  * SwiGLU into `hbuf`, 2 = down projection from `hbuf` into `out`, 3 = both.
  * Lets a caller put other work (a transfer on another stream) between the
- * passes of the shared expert.  CTA-pair kernel only. */
+ * passes of the shared expert.  `stages` is the depth of the kernel's
+ * shared-memory pipeline, 2..6 (0 = 6): with 5 an SM keeps enough shared memory
+ * and registers free for one CTA of sb_router_topk launched on another stream,
+ * which is how the router is hidden behind the shared expert's gate/up pass. */
 int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,
                                  const void *w13, const void *w2, const int32_t *slot_of_expert,
                                  const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
-                                 void *hbuf, void *out, int32_t passes, int32_t *status, void *stream);
+                                 void *hbuf, void *out, int32_t passes, int32_t stages, int32_t *status,
+                                 void *stream);
 
 /* Token counts up to this use the weight-streaming kernels below inside
  * sb_moe_layer_forward instead of the tensor-core grouped GEMM. */
@@ -347,6 +374,14 @@ int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_
  * same flags. */
 int32_t sb_ep_barrier_seq(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
                           int32_t *status, void *stream);
+/* sb_ep_barrier_seq with the wait limit given by the caller (nanoseconds of the
+ * device's global timer, > 0) instead of the default 2 s: a host that polls
+ * peer liveness can keep a lost rank from holding the stream for seconds.  On
+ * expiry `status` becomes 3, the kernel returns and the context stays usable.
+ * The reference's counterpart is the process-group timeout of its collectives
+ * (utils/eval_core.py:7041-7056). */
+int32_t sb_ep_barrier_timed(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
+                            uint64_t limit_ns, int32_t *status, void *stream);
 
 /* From the complete counts matrix: where this rank's items of each expert start
  * in the destination's receive buffer (`dst_base` [E]), and this rank's own
@@ -383,7 +418,10 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
  * [recv_cap] bf16) and remember where it went (`item_rank`, `item_row` [n_items]).
  * `slot_of_item` / `local_offsets` come from sb_permute on the local items.
  * With `peer_meta` (int32 [recv_cap] per rank, may be NULL) every row also
- * carries its return address: (rank << 24) | item index, n_items < 2^24. */
+ * carries its return address: (rank << 24) | item index, n_items < 2^24, and
+ * `item_row[i]` is then the item's row in this rank's own return buffer (= i)
+ * instead of its row at the owner.  Either way an item that was not sent
+ * (expert id outside [0,E), no room) has item_rank = item_row = -1. */
 int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *item_scale,
                        const int32_t *slot_of_item, const int32_t *local_offsets,
                        const int32_t *dst_base, const int32_t *owner, int32_t n_items,
@@ -400,7 +438,8 @@ int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *it
  * sender is another GPU) while the GEMM is still running, instead of to a
  * local buffer that the senders read afterwards.  After the next barrier each
  * sender combines its own return buffer with sb_combine (slot_of_item =
- * identity).  Replaces the output all-to-all of utils/eval_core.py:15048-15054
+ * the `item_row` that sb_ep_dispatch wrote: the item's own index, or -1 for an
+ * item that was never sent, which the combine skips).  Replaces the output all-to-all of utils/eval_core.py:15048-15054
  * together with the segment compute of 13156-13372. */
 int32_t sb_ep_resolve_return(const int32_t *recv_meta, const int32_t *recv_offsets, int32_t E,
                              void *const *peer_ret, int32_t ep, int32_t ret_rows, int32_t H, int32_t recv_cap,
@@ -454,7 +493,10 @@ size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K,
 
 /*
  * One whole single-GPU layer pass: router -> permute -> routed grouped SwiGLU
- * -> shared expert -> combine, all on `stream`, without a host sync.
+ * -> shared expert -> combine, without a host sync; ordered on `stream` (with
+ * a shared expert, router and sort run on the library's side stream between a
+ * fork from and a join back into `stream`, so the call can be captured in a
+ * CUDA graph).  Needs sb_init(device) once per device.
  * Replaces `DistributedSparseMoeBlock.forward` at world=1
  * (utils/eval_core.py:16418-16563 with 14690-14721 and 9455-9463).
  * `status` is a device int32 (may be NULL) as in sb_grouped_swiglu.

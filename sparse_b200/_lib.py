@@ -46,6 +46,8 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_last_error_string": (C.c_char_p, []),
     "sb_device_sm_count": (i32, []),
     "sb_last_launch_count": (i32, []),
+    "sb_init": (i32, [i32]),
+    "sb_set_tuning": (i32, [C.c_char_p, i32]),
     "sb_tile_rows": (i32, []),
     "sb_w13_interleaved": (i32, []),
     "sb_router_topk": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
@@ -71,6 +73,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_publish_counts": (i32, [vp, i32, i32, i32, C.POINTER(vp), vp]),
     "sb_ep_barrier": (i32, [C.POINTER(vp), i32, i32, C.c_uint32, vp, vp]),
     "sb_ep_barrier_seq": (i32, [C.POINTER(vp), i32, i32, vp, vp, vp]),
+    "sb_ep_barrier_timed": (i32, [C.POINTER(vp), i32, i32, vp, C.c_uint64, vp, vp]),
     "sb_ep_exchange_dispatch": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp,
                                       vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp,
                                       C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),
@@ -78,7 +81,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                              C.POINTER(vp), C.POINTER(vp), vp, vp, i32, C.POINTER(vp), vp]),
     "sb_ep_return_rows": (i32, [vp, vp, vp, i32, i32, i32, vp]),
-    "sb_grouped_swiglu_passes": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp]),
+    "sb_grouped_swiglu_passes": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp]),
     "sb_ep_resolve_return": (i32, [vp, vp, i32, C.POINTER(vp), i32, i32, i32, i32, vp, vp]),
     "sb_grouped_swiglu_scatter": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_combine": (i32, [C.POINTER(vp), vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
@@ -104,6 +107,16 @@ def _load() -> C.CDLL:
 lib = _load()
 if lib.sb_moe_layer_struct_bytes() != C.sizeof(MoeLayer):
     raise ImportError("sparse_b200: struct sb_moe_layer of the library and its ctypes mirror differ")
+
+
+_initialised = set()
+
+
+def init_device(index: int) -> None:
+    """`sb_init` once per device index (creates the library's side stream there)."""
+    if index not in _initialised:
+        check(lib.sb_init(int(index)), "sb_init")
+        _initialised.add(index)
 
 
 def check(status: int, what: str) -> None:

@@ -25,7 +25,7 @@ class B200MoeBlock:
     def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int,
                  norm_topk_prob: bool = False, fp32_router_logits: bool = False,
                  return_router_logits: bool = True, ep_rank: int = 0, ep_size: int = 1,
-                 process_group=None, owner=None):
+                 process_group=None, owner=None, use_graphs: bool = False):
         self.weights = weights
         self.device = weights.device
         self.top_k = top_k
@@ -41,11 +41,16 @@ class B200MoeBlock:
                                            fp32_logits=fp32_router_logits)
         self._x_stage: Optional[torch.Tensor] = None
         self.last_launches = 0
+        # Replay each (input buffer, output buffer) pair's step from a CUDA graph
+        # (see `forward_device`); off by default because a graph pins its buffers.
+        self.use_graphs = use_graphs
+        self._graphs = {}
 
     @classmethod
     def from_block_weights(cls, w, device: torch.device, ep_rank: int = 0, ep_size: int = 1,
                            max_tokens: int = 4096, process_group=None, placement=None,
-                           layer_idx: int = 0, stage: str = "prefill") -> "B200MoeBlock":
+                           layer_idx: int = 0, stage: str = "prefill",
+                           use_graphs: bool = False) -> "B200MoeBlock":
         """Build from seeded `synth.BlockWeights`; at ep_size > 1 only the
         experts this rank serves are loaded: round-robin (e % ep_size) by default,
         or every expert a `placement.Placement` lists `ep_rank` as a replica of,
@@ -71,17 +76,55 @@ class B200MoeBlock:
                 lw.set_shared(w.sh_gate, w.sh_up, w.sh_down, w.sh_scalar_gate)
         return cls(lw, s.top_k, max_tokens, norm_topk_prob=s.norm_topk_prob,
                    fp32_router_logits=not s.shared_gate and s.num_experts == 64,
-                   ep_rank=ep_rank, ep_size=ep_size, process_group=process_group, owner=owner)
+                   ep_rank=ep_rank, ep_size=ep_size, process_group=process_group, owner=owner,
+                   use_graphs=use_graphs)
 
     # -- the three entry points -----------------------------------------------------
     def forward_device(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One layer pass on device-resident rows.  With `use_graphs` the launches
+        of a pass are recorded once per (input buffer, row count, output buffer)
+        and replayed afterwards: a serving loop that cycles through a few fixed
+        buffers pays one graph launch per step instead of ten to twenty kernel
+        launches from Python.  The first pass on new buffers runs un-recorded
+        (one-time set-up must not be captured); under expert parallelism every
+        rank has to make the same sequence of calls."""
         if self._ep is not None:
-            res = self._ep.forward(x, out)
+            if self.use_graphs and self._warm:
+                res = self._ep.forward_graphed(x, out)
+            else:
+                res = self._ep.forward(x, out)
+                self._warm = True
             self.last_launches = self._ep.last_launches
             return res
+        if self.use_graphs and self._warm and x.shape[0] <= self.runner.max_tokens:
+            return self._forward_graphed_local(x, out)
         res, _, _, _ = self.runner.forward(x, out)
+        self._warm = True
         self.last_launches = self.runner.last_launches
         return res
+
+    _warm = False
+
+    def _forward_graphed_local(self, x: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+        dst = self.runner.out[:x.shape[0]] if out is None else out
+        key = (x.data_ptr(), x.shape[0], dst.data_ptr())
+        ent = self._graphs.get(key)
+        if ent is None:
+            if len(self._graphs) >= 32:
+                self._graphs.clear()
+            stream = torch.cuda.current_stream(self.device)
+            cap = torch.cuda.Stream(device=self.device)
+            cap.wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap):
+                with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
+                    self.runner.forward(x, dst)
+            stream.wait_stream(cap)
+            ent = (graph, self.runner.last_launches, x, dst)
+            self._graphs[key] = ent
+        ent[0].replay()
+        self.last_launches = ent[1]
+        return ent[3]
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """x_host, out_host: pinned bf16 [T,H].  Copies in, runs the layer, copies

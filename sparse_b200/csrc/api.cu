@@ -5,6 +5,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "sb_common.cuh"
@@ -32,12 +33,12 @@ void reset_launch_count() { g_launches = 0; }
 
 static inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Side stream and fork/join events for the light-group kernels, one set per
-// device, created on first use.  Holding the mutex over a fork..join enqueue
-// keeps two host threads from interleaving their records on the shared events.
+// Side stream and fork/join events of the layer driver, one set per device,
+// created by sb_init.  Holding the mutex over a fork..join enqueue keeps two
+// host threads from interleaving their records on the shared events.
 struct SideLane {
   cudaStream_t stream = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
+  cudaEvent_t fork = nullptr, mid = nullptr, join = nullptr;
 };
 static std::recursive_mutex g_side_mu;
 static SideLane g_side[64];
@@ -46,30 +47,36 @@ static SideLane *side_lane() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   SideLane &l = g_side[dev];
-  if (l.stream == nullptr) {
-    if (cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) != cudaSuccess) { l.stream = nullptr; return nullptr; }
-    if (cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
-      cudaStreamDestroy(l.stream);
-      l.stream = nullptr;
-      return nullptr;
-    }
-  }
-  return &l;
+  return l.stream != nullptr ? &l : nullptr;
 }
 
-static bool overlap_sort() {
-  static const bool v = [] {
-    const char *e = getenv("SPARSE_B200_OVERLAP_SORT");
-    return !(e && strcmp(e, "0") == 0);
-  }();
-  return v;
+static int32_t create_side_lane(int dev) {
+  std::lock_guard<std::recursive_mutex> lock(g_side_mu);
+  SideLane &l = g_side[dev];
+  if (l.stream != nullptr) return SB_OK;
+  cudaStream_t st = nullptr;
+  SB_CUDA_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  for (int i = 0; i < 3; ++i) {
+    if (cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(ev[j]);
+      cudaStreamDestroy(st);
+      return fail(SB_E_CUDA, "sb_init: cannot create the layer driver's events");
+    }
+  }
+  l.fork = ev[0]; l.mid = ev[1]; l.join = ev[2];
+  l.stream = st;
+  return SB_OK;
 }
 
 static int env_int(const char *name, int fallback) {
   const char *e = getenv(name);
   return (e && *e) ? atoi(e) : fallback;
 }
+// Router and sort beside the shared expert's gate/up pass (1, default) or the
+// router in front of everything and only the sort beside the shared expert (0).
+static std::atomic<int> g_router_overlap{1};
+static int router_overlap() { return g_router_overlap.load(std::memory_order_relaxed); }
 // Largest batch for which the shared and the routed GEMM share the SMs by grid
 // size, and how many CTA pairs the shared expert gets then.
 static int split_tokens() {
@@ -81,48 +88,18 @@ static int shared_pairs() {
   return v;
 }
 
-static int hybrid_rows() {
-  static const int v = [] {
-    const char *e = getenv("SPARSE_B200_HYBRID");
-    return (e && strcmp(e, "1") == 0) ? SB_DECODE_MAX_TOKENS : 0;
-  }();
-  return v;
-}
+// Pipeline depth of a GEMM launch that should leave room for a router CTA on
+// every SM (see grouped_swiglu_pair.cu).
+constexpr int kStagesBesideRouter = 5;
 
-// The grouped expert MLP.  Experimental split, off unless SPARSE_B200_HYBRID=1:
-// with the CTA-pair kernel and a tile table, groups of at most 16 rows go to
-// the weight-streaming kernels on a side stream while the tensor-core kernel
-// works on the rest.  Measured on B200 it loses to the tile kernel alone (one
-// streaming CTA per SM beside a GEMM CTA moves 1.7 TB/s; the tile kernel
-// already hides most light tiles behind heavy ones), so it is not the default.
 int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, int dense_rows,
                                   const void *w13, const void *w2, const int32_t *slot_of_expert,
                                   const void *row_scale, int R_cap, int H, int I, int S, void *hbuf,
-                                  void *out, int32_t *status, cudaStream_t stream, int max_pairs = 0) {
-  if (!sb_w13_interleaved())
-    return launch_grouped_swiglu(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
-                                 H, I, S, hbuf, out, status, stream);
-  const int light = (tile_table != nullptr && H % 32 == 0 && I % 32 == 0) ? hybrid_rows() : 0;
-  if (light == 0)
-    return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
-                                      R_cap, H, I, S, hbuf, out, status, 0, max_pairs, nullptr, stream);
-  std::lock_guard<std::recursive_mutex> lock(g_side_mu);
-  SideLane *lane = side_lane();
-  if (lane == nullptr) return fail(SB_E_CUDA, "sb_grouped_swiglu: cannot create the side stream");
-  SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
-  SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
-  int32_t rc = launch_decode_experts(rows, nullptr, 1, tile_table, slot_of_expert, w13, w2, row_scale, H, I, S,
-                                     hbuf, out, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status, 1, 0,
-                                     nullptr, nullptr, lane->stream);
-  // the join is recorded even after a failed launch, so the side stream never
-  // stays forked from a stream that is being captured
-  SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
-  int32_t rc2 = SB_OK;
-  if (rc == SB_OK)
-    rc2 = launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap,
-                                     H, I, S, hbuf, out, status, light, 0, nullptr, stream);
-  SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
-  return rc != SB_OK ? rc : rc2;
+                                  void *out, int32_t *status, cudaStream_t stream, int max_pairs = 0,
+                                  int passes = 3, int stages = 0) {
+  return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale,
+                                    R_cap, H, I, S, hbuf, out, status, 0, max_pairs, nullptr, stream, passes,
+                                    stages);
 }
 
 // Carves the caller's workspace; the same walk gives the required size.
@@ -161,28 +138,127 @@ static LayerScratch carve(char *base, int T, int H, int E, int K, int I, int I_s
   return s;
 }
 
+// Layer pass above the decode size.  The shared expert's gate/up pass needs
+// nothing from the routing and its down pass only the scalar gate, so with a
+// shared expert the work is split over two streams:
+//
+//   caller's stream   shared gate/up (5-stage pipeline) . shared down .        . routed GEMMs . combine
+//   side stream       router . count/scan/scatter/gather ^(mid)        ^(join)
+//
+// The gate/up launch goes first and takes one CTA per SM with a pipeline one
+// stage shorter than usual; what it leaves free on each SM (shared memory,
+// registers) is what one router CTA needs, so the router's CUDA-core dot
+// products run under the tensor-core pass instead of in front of it.  Up to
+// split_tokens() rows, where both GEMMs stream weights and neither fills the
+// machine, the routed GEMM follows on the side stream too and the two share
+// the SMs by grid size.  Without a shared expert everything runs in order on
+// the caller's stream.
+static int32_t layer_forward_large(const sb_moe_layer *L, const LayerScratch &s, int32_t *status,
+                                   cudaStream_t stream) {
+  const int T = L->T, H = L->H, E = L->E, K = L->K, I = L->I, Is = L->I_shared;
+  void *shared_scale = L->shared_gate_w ? s.shared_scale : nullptr;
+  int32_t rc;
+  if (Is == 0) {
+    rc = launch_router(L->x, L->router_w, L->router_bias, nullptr, T, H, E, K, L->renorm, SB_DTYPE_BF16,
+                       L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits, nullptr, stream);
+    if (rc != SB_OK) return rc;
+    rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes, s.xs,
+                        s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale, s.tile_table, stream);
+    if (rc != SB_OK) return rc;
+    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale, s.r_cap,
+                                   H, I, L->n_slots, s.hbuf, s.y, status, stream);
+    if (rc != SB_OK) return rc;
+    return launch_combine(s.y, s.slot_of_item, L->topk_idx, nullptr, T, H, K, L->out, stream);
+  }
+  std::unique_lock<std::recursive_mutex> lock(g_side_mu);
+  SideLane *lane = side_lane();
+  if (lane == nullptr)
+    return fail(SB_E_INVALID_ARG, "sb_moe_layer_forward: call sb_init(device) once for this device first");
+  const bool beside = router_overlap() != 0;
+  const int all_pairs = sb_device_sm_count() / 2;
+  const bool split = T <= split_tokens() && all_pairs > 2 * shared_pairs();
+  cudaStream_t side = lane->stream;
+  if (!beside) {
+    rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm, SB_DTYPE_BF16,
+                       L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits, shared_scale, stream);
+    if (rc != SB_OK) return rc;
+  }
+  SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
+  SB_CUDA_CHECK(cudaStreamWaitEvent(side, lane->fork, 0));
+  // From here on the side stream is forked from the caller's: every path below
+  // records `mid` and `join` and makes the caller's stream wait for both, so a
+  // stream capture always ends joined, whatever failed in between.
+  int32_t rc_shared = SB_OK;
+  if (beside)
+    rc_shared = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr, nullptr, T, H, Is,
+                                          1, s.shared_h, s.shared_out, status, stream,
+                                          split ? shared_pairs() : 0, 1, kStagesBesideRouter);
+  rc = SB_OK;
+  if (beside)
+    rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm, SB_DTYPE_BF16,
+                       L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits, shared_scale, side);
+  SB_CUDA_CHECK(cudaEventRecord(lane->mid, side));
+  if (rc == SB_OK)
+    rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes, s.xs,
+                        s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale, s.tile_table, side);
+  if (rc == SB_OK && split)
+    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale, s.r_cap,
+                                   H, I, L->n_slots, s.hbuf, s.y, status, side, all_pairs - shared_pairs());
+  SB_CUDA_CHECK(cudaEventRecord(lane->join, side));
+  SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->mid, 0));
+  if (rc_shared == SB_OK)
+    rc_shared = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr, shared_scale, T,
+                                          H, Is, 1, s.shared_h, s.shared_out, status, stream,
+                                          split ? shared_pairs() : 0, beside ? 2 : 3, 0);
+  SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
+  lock.unlock();
+  if (rc != SB_OK) return rc;
+  if (rc_shared != SB_OK) return rc_shared;
+  if (!split) {
+    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale, s.r_cap,
+                                   H, I, L->n_slots, s.hbuf, s.y, status, stream);
+    if (rc != SB_OK) return rc;
+  }
+  return launch_combine(s.y, s.slot_of_item, L->topk_idx, s.shared_out, T, H, K, L->out, stream);
+}
+
 }  // namespace sb
 
 using namespace sb;
 
 extern "C" {
 
-int32_t sb_abi_version(void) { return 1; }
+int32_t sb_abi_version(void) { return 2; }
 
-// Which grouped-GEMM kernel this process uses: the CTA-pair kernel
-// (SPARSE_B200_GEMM=pair) or the single-CTA kernel (=single).  Read once.
-static int gemm_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char *v = getenv("SPARSE_B200_GEMM");
-    mode = (v != nullptr && strcmp(v, "single") == 0) ? 0 : 1;   // default: CTA-pair kernel
-  }
-  return mode;
+int32_t sb_init(int32_t device) {
+  int count = 0;
+  SB_CUDA_CHECK(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count || device >= 64)
+    return fail(SB_E_INVALID_ARG, "sb_init: device %d outside [0,%d)", device, count < 64 ? count : 64);
+  int prev = -1;
+  SB_CUDA_CHECK(cudaGetDevice(&prev));
+  SB_CUDA_CHECK(cudaSetDevice(device));
+  int32_t rc = create_side_lane(device);
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  return rc;
 }
 
-int32_t sb_tile_rows(void) { return gemm_mode() == 1 ? 256 : SB_TILE_M; }
+int32_t sb_set_tuning(const char *key, int32_t value) {
+  if (!key) return fail(SB_E_INVALID_ARG, "sb_set_tuning: null key");
+  if (strcmp(key, "router_overlap") == 0) {
+    if (value != 0 && value != 1) return fail(SB_E_INVALID_ARG, "sb_set_tuning: router_overlap must be 0 or 1");
+    g_router_overlap.store(value);
+    return SB_OK;
+  }
+  int32_t rc = set_gemm_tuning(key, value);
+  if (rc == SB_E_UNSUPPORTED) return fail(SB_E_INVALID_ARG, "sb_set_tuning: unknown key '%s'", key);
+  return rc;
+}
 
-int32_t sb_w13_interleaved(void) { return gemm_mode() == 1 ? 1 : 0; }
+/* Rows per tile-table entry and the row order of w13: constants of the CTA-pair GEMM. */
+int32_t sb_tile_rows(void) { return 256; }
+
+int32_t sb_w13_interleaved(void) { return 1; }
 
 const char *sb_last_error_string(void) { return g_err; }
 
@@ -247,12 +323,12 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
 int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,
                                  const void *w13, const void *w2, const int32_t *slot_of_expert,
                                  const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
-                                 void *hbuf, void *out, int32_t passes, int32_t *status, void *stream) {
+                                 void *hbuf, void *out, int32_t passes, int32_t stages, int32_t *status,
+                                 void *stream) {
   if (passes < 1 || passes > 3) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_passes: passes=%d", passes);
-  if (!sb_w13_interleaved())
-    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_passes: needs the CTA-pair kernel (SPARSE_B200_GEMM=pair)");
   return launch_grouped_swiglu_pair(rows, tile_table, dense_rows, w13, w2, slot_of_expert, row_scale, R_cap, H, I,
-                                    S, hbuf, out, status, 0, 0, nullptr, static_cast<cudaStream_t>(stream), passes);
+                                    S, hbuf, out, status, 0, 0, nullptr, static_cast<cudaStream_t>(stream), passes,
+                                    stages);
 }
 
 int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, const void *w13, const void *w2,
@@ -260,8 +336,6 @@ int32_t sb_grouped_swiglu_scatter(const void *rows, const int32_t *tile_table, c
                                   int32_t H, int32_t I, int32_t S, void *hbuf, const uint64_t *row_dst,
                                   int32_t *status, void *stream) {
   if (!tile_table || !row_dst) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_scatter: null pointer");
-  if (!sb_w13_interleaved())
-    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_scatter: needs the CTA-pair kernel (SPARSE_B200_GEMM=pair)");
   return launch_grouped_swiglu_pair(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S, hbuf,
                                     nullptr, status, 0, 0, reinterpret_cast<const unsigned long long *>(row_dst),
                                     static_cast<cudaStream_t>(stream));
@@ -277,12 +351,12 @@ int32_t sb_grouped_swiglu_mixed(const void *rows, const int32_t *tile_table, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!tile_table) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: needs a tile table");
   const unsigned long long *dst = reinterpret_cast<const unsigned long long *>(row_dst);
-  if (dst != nullptr && !sb_w13_interleaved())
-    return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_mixed: row_dst needs the CTA-pair kernel build");
   const bool with_shared = shared_w13 != nullptr && T > 0;
   if (with_shared && (!shared_x || !shared_w2 || !shared_h || !shared_out || I_shared <= 0))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu_mixed: shared expert arguments go together");
-  if (!sb_w13_interleaved() || H % 32 != 0 || I % 32 != 0 || (with_shared && I_shared % 32 != 0)) {
+  if (H % 32 != 0 || I % 32 != 0 || (with_shared && I_shared % 32 != 0)) {
+    if (dst != nullptr)
+      return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu_mixed: row_dst needs H, I, I_shared to be multiples of 32");
     int32_t rc = launch_grouped_swiglu_any(rows, tile_table, 0, w13, w2, slot_of_expert, row_scale, R_cap, H, I, S,
                                            hbuf, out, status, st);
     if (rc != SB_OK || !with_shared) return rc;
@@ -366,18 +440,12 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
   if (L->ws_bytes < s.total)
     return fail(SB_E_WORKSPACE, "sb_moe_layer_forward: workspace %zu < %zu bytes", L->ws_bytes, s.total);
 
-  int32_t rc;
-  if (T <= SB_DECODE_MAX_TOKENS)
-    rc = launch_router_decode(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
-                              L->router_fp32_logits, s.router_ws, L->topk_idx, L->topk_w, L->logits,
-                              L->shared_gate_w ? s.shared_scale : nullptr, s.expert_offsets, s.slot_of_item,
-                              s.item_of_slot, s.slot_scale, s.tile_table, stream);
-  else
-    rc = launch_router(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
-                       SB_DTYPE_BF16, L->router_fp32_logits, L->topk_idx, L->topk_w, L->logits,
-                       L->shared_gate_w ? s.shared_scale : nullptr, stream);
-  if (rc != SB_OK) return rc;
   if (T <= SB_DECODE_MAX_TOKENS) {
+    int32_t rc = launch_router_decode(L->x, L->router_w, L->router_bias, L->shared_gate_w, T, H, E, K, L->renorm,
+                                      L->router_fp32_logits, s.router_ws, L->topk_idx, L->topk_w, L->logits,
+                                      L->shared_gate_w ? s.shared_scale : nullptr, s.expert_offsets,
+                                      s.slot_of_item, s.item_of_slot, s.slot_scale, s.tile_table, stream);
+    if (rc != SB_OK) return rc;
     // decode-sized pass: the router launch already sorted the items (no gathered copy of x)
     rc = launch_decode_experts(L->x, s.item_of_slot, K, s.tile_table, L->slot_of_expert, L->w13, L->w2,
                                s.slot_scale, H, I, L->n_slots, s.hbuf, s.y, Is > 0 ? L->shared_w13 : nullptr,
@@ -387,54 +455,7 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *L, int32_t *status, void *strea
     return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
                           L->out, stream);
   }
-  // The shared expert needs nothing from the routing: it runs on the caller's
-  // stream while count/scan/scatter/gather run beside it on the library's side
-  // stream.  Up to split_tokens() rows, where both GEMMs stream weights and
-  // neither fills the machine, the routed GEMM follows on the side stream too
-  // and the two share the SMs by grid size (a few CTA pairs for the shared
-  // expert's few tiles, the rest for the routed groups); above that they run
-  // one after the other on all SMs.
-  SideLane *lane = nullptr;
-  std::unique_lock<std::recursive_mutex> lock(g_side_mu, std::defer_lock);
-  if (Is > 0 && overlap_sort()) {
-    lock.lock();
-    lane = side_lane();
-  }
-  const int all_pairs = sb_device_sm_count() / 2;
-  const bool split = lane != nullptr && sb_w13_interleaved() && T <= split_tokens() && hybrid_rows() == 0 &&
-                     all_pairs > 2 * shared_pairs();
-  cudaStream_t side = stream;
-  if (lane != nullptr) {
-    SB_CUDA_CHECK(cudaEventRecord(lane->fork, stream));
-    SB_CUDA_CHECK(cudaStreamWaitEvent(lane->stream, lane->fork, 0));
-    side = lane->stream;
-  }
-  rc = launch_permute(L->x, L->topk_idx, L->topk_w, T * K, K, H, E, s.permute_ws, s.permute_ws_bytes,
-                      s.xs, s.expert_offsets, s.slot_of_item, s.item_of_slot, s.slot_scale,
-                      s.tile_table, side);
-  if (rc == SB_OK && split)
-    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
-                                   s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, side,
-                                   all_pairs - shared_pairs());
-  if (lane != nullptr) SB_CUDA_CHECK(cudaEventRecord(lane->join, lane->stream));
-  int32_t rc_shared = SB_OK;
-  if (rc == SB_OK && Is > 0)
-    rc_shared = launch_grouped_swiglu_any(L->x, nullptr, T, L->shared_w13, L->shared_w2, nullptr,
-                                          L->shared_gate_w ? s.shared_scale : nullptr, T, H, Is, 1, s.shared_h,
-                                          s.shared_out, status, stream, split ? shared_pairs() : 0);
-  if (lane != nullptr) {
-    SB_CUDA_CHECK(cudaStreamWaitEvent(stream, lane->join, 0));
-    lock.unlock();
-  }
-  if (rc != SB_OK) return rc;
-  if (rc_shared != SB_OK) return rc_shared;
-  if (!split) {
-    rc = launch_grouped_swiglu_any(s.xs, s.tile_table, 0, L->w13, L->w2, L->slot_of_expert, s.slot_scale,
-                                   s.r_cap, H, I, L->n_slots, s.hbuf, s.y, status, stream);
-    if (rc != SB_OK) return rc;
-  }
-  return launch_combine(s.y, s.slot_of_item, L->topk_idx, Is > 0 ? s.shared_out : nullptr, T, H, K,
-                        L->out, stream);
+  return layer_forward_large(L, s, status, stream);
 }
 
 }  // extern "C"

@@ -70,7 +70,8 @@ __global__ void ep_publish_kernel(const int32_t *__restrict__ local_offsets, int
 // Thread p < ep tells peer p "this rank reached `epoch`" and waits for peer p's
 // flag to reach it; the wait is bounded.
 __device__ __forceinline__ void barrier_body(const PeerPtrs &flags, int rank, int ep, uint32_t epoch,
-                                             int32_t *__restrict__ status) {
+                                             int32_t *__restrict__ status,
+                                             unsigned long long limit_ns = kBarrierLimitNs) {
   const int p = threadIdx.x;
   if (p >= ep) return;
   __threadfence_system();
@@ -82,7 +83,7 @@ __device__ __forceinline__ void barrier_body(const PeerPtrs &flags, int rank, in
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if ((int32_t)(v - epoch) >= 0) break;
-    if (gtimer_ns() - t0 > kBarrierLimitNs) {
+    if (gtimer_ns() - t0 > limit_ns) {
       if (status) atomicExch(status, 3);
       break;
     }
@@ -102,9 +103,9 @@ __device__ __forceinline__ uint32_t next_epoch(uint32_t *counter) {
 }
 
 __global__ void ep_barrier_kernel(PeerPtrs flags, int rank, int ep, uint32_t epoch, uint32_t *epoch_counter,
-                                  int32_t *__restrict__ status) {
+                                  int32_t *__restrict__ status, unsigned long long limit_ns) {
   if (epoch_counter != nullptr) epoch = next_epoch(epoch_counter);
-  barrier_body(flags, rank, ep, epoch, status);
+  barrier_body(flags, rank, ep, epoch, status, limit_ns);
 }
 
 // One CTA.  Reads the complete counts matrix of this rank and writes
@@ -212,7 +213,9 @@ __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const
       static_cast<__nv_bfloat16 *>(recv_scale.p[d])[row] = item_scale[i];
       // return address of the row: sender rank and the sender's item index
       if (recv_meta != nullptr) static_cast<int32_t *>(recv_meta->p[d])[row] = (rank << 24) | i;
-      item_rank[i] = d; item_row[i] = row;
+      // with return addresses the result comes back into row i of this rank's
+      // return buffer: that is the row the local combine reads (-1 above = skip)
+      item_rank[i] = d; item_row[i] = recv_meta != nullptr ? i : row;
     }
   }
 }
@@ -443,21 +446,29 @@ int32_t sb_ep_barrier(void *const *peer_flags, int32_t rank, int32_t ep, uint32_
   PeerPtrs pf;
   int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier");
   if (rc != SB_OK) return rc;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, epoch, nullptr, status);
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, epoch, nullptr, status,
+                                                                      kBarrierLimitNs);
+  SB_LAUNCH_CHECK();
+  return SB_OK;
+}
+
+int32_t sb_ep_barrier_timed(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
+                            uint64_t limit_ns, int32_t *status, void *stream) {
+  if (rank < 0 || rank >= ep || !epoch_counter || limit_ns == 0)
+    return fail(SB_E_INVALID_ARG, "sb_ep_barrier_timed: rank=%d ep=%d limit=%llu ns", rank, ep,
+                (unsigned long long)limit_ns);
+  PeerPtrs pf;
+  int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier_timed");
+  if (rc != SB_OK) return rc;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, 0u, epoch_counter, status,
+                                                                      (unsigned long long)limit_ns);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
 
 int32_t sb_ep_barrier_seq(void *const *peer_flags, int32_t rank, int32_t ep, uint32_t *epoch_counter,
                           int32_t *status, void *stream) {
-  if (rank < 0 || rank >= ep || !epoch_counter)
-    return fail(SB_E_INVALID_ARG, "sb_ep_barrier_seq: rank=%d ep=%d", rank, ep);
-  PeerPtrs pf;
-  int32_t rc = fill_peers(&pf, peer_flags, ep, "sb_ep_barrier_seq");
-  if (rc != SB_OK) return rc;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, ep, 0u, epoch_counter, status);
-  SB_LAUNCH_CHECK();
-  return SB_OK;
+  return sb_ep_barrier_timed(peer_flags, rank, ep, epoch_counter, kBarrierLimitNs, status, stream);
 }
 
 int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_counts, void *const *peer_flags,

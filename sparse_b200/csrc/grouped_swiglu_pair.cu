@@ -1,7 +1,9 @@
-// Grouped bf16 SwiGLU expert MLP, CTA-pair edition (tcgen05 cta_group::2).
+// Grouped bf16 SwiGLU expert MLP on CTA pairs (tcgen05 cta_group::2).
 //
-// Same arithmetic and rounding points as grouped_swiglu.cu; different mapping
-// onto the machine, chosen for ragged expert groups:
+// Arithmetic and rounding points of the reference's expert forward
+// (utils/eval_core.py:11787-11790, route weight at 11765): fp32 accumulation,
+// bf16 rounding after gate, up, silu, product, down and the route-weight
+// scaling.  Mapping onto the machine, chosen for ragged expert groups:
 //
 //  * operands are swapped: the WEIGHT rows fill the 256-row M dimension of the
 //    MMA (always full), the TOKENS of one expert are the N dimension, which the
@@ -12,8 +14,15 @@
 //    (32 KB instead of 48 KB per CTA for the same flops), the tensor cores read
 //    the token half of the peer through distributed shared memory.  That cuts
 //    L2->SM traffic by a third, which is what capped the single-CTA kernel.
-//  * six 36 KB stages (one K step of a full tile, or two K steps of a tile of
-//    at most 32 tokens); TMEM holds two 128-lane x 256-column accumulators per CTA.
+//  * up to six 36 KB stages (one K step of a full tile, or two K steps of a tile
+//    of at most 32 tokens); TMEM holds two 128-lane x 256-column accumulators per
+//    CTA.  A launch may ask for fewer stages so that a CTA of another kernel
+//    (the router) fits on the SM beside it.
+//  * tiles are not walked in table order: every CTA ranks the table's row chunks
+//    by size (largest first, ties in table order) and the pairs deal the ranked
+//    tiles out boustrophedon (pair 0..P-1, then P-1..0, ...).  Each pair gets
+//    the same mix of heavy and light tiles, heaviest first, which a fixed
+//    stride over a Zipf-shaped table does not give (tile cost varies 16x).
 //  * pass 1 reads the gate/up slab with gate and up rows interleaved
 //    (row 2j = gate_j, row 2j+1 = up_j), so the two values a SwiGLU output
 //    needs sit in adjacent TMEM lanes = adjacent threads: one shuffle, no
@@ -27,9 +36,13 @@
 // owner (and, in the leader CTA, lane 0 = MMA issuer), warps 2-9 = epilogue.
 // All mbarrier waits are bounded (2 s); on expiry the CTA sets an abort flag,
 // reports through `status`, drains, joins the cluster barrier, frees TMEM.
+// A chunk whose expert has no resident weight slot raises status 2 and is
+// skipped by all three roles: nothing is computed with another expert's weights.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "sb_common.cuh"
@@ -46,7 +59,6 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 320;         // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = kRowsPerCta * kBlockK * 2;      // 16 KB
-constexpr uint32_t kBBytes = (kMaxN / 2) * kBlockK * 2;      // 16 KB (this CTA's half of the tokens)
 constexpr uint32_t kLightTokBytes = 16 * kBlockK * 2;         // 2 KB: a 16-row token box of one K step
 // A stage holds one K step of a full tile (A 16 KB + B up to 16 KB) or, for a
 // light tile (at most 16 tokens per CTA), TWO K steps (A, A', then the two
@@ -55,7 +67,10 @@ constexpr uint32_t kLightTokBytes = 16 * kBlockK * 2;         // 2 KB: a 16-row 
 constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kLightTokBytes;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kScatterTileBytes = 16 * kRowsPerCta * 2;    // 16 tokens x this CTA's 128 output columns, bf16
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * kScatterTileBytes;
+constexpr int kMaxSched = 768;          // row chunks that can be ranked (larger tables are walked in table order)
+constexpr uint32_t kTailBytes = 256 + 2 * kScatterTileBytes + kMaxSched * 2;   // barriers, scatter staging, chunk order
+__host__ __device__ constexpr uint32_t smem_bytes(int stages) { return (uint32_t)stages * kStageBytes + 1024 + kTailBytes; }
+static_assert(smem_bytes(kStages) <= 232448, "shared memory of a CTA");
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kSlotSkip = -2;
 constexpr int kModeSwiglu = 0, kModeScale = 1;
@@ -174,12 +189,13 @@ __device__ __forceinline__ uint32_t idesc_m256(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileW >> 4) << 24);
 }
 
-struct Chunk { int slot, tok_begin, tok_end; };
+struct Chunk { int slot, tok_begin, tok_end; bool absent; };
 
 __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense_rows,
                                             const int32_t *slot_of_expert, int c, int skip_rows_upto,
-                                            int dense_chunk) {
+                                            int dense_chunk, int n_slots) {
   Chunk t;
+  t.absent = false;
   if (tile_table == nullptr) {
     t.slot = 0;
     t.tok_begin = c * dense_chunk;
@@ -189,10 +205,52 @@ __device__ __forceinline__ Chunk read_chunk(const int32_t *tile_table, int dense
     t.slot = slot_of_expert ? __ldg(slot_of_expert + e.x) : e.x;
     t.tok_begin = e.y;
     t.tok_end = e.z;
-    if (e.z - e.y <= skip_rows_upto) t.slot = kSlotSkip;      // light group: the streaming kernels' work
+    if (e.z - e.y <= skip_rows_upto) {
+      t.slot = kSlotSkip;                                        // light group: the streaming kernels' work
+    } else if (t.slot != kSlotSkip && (t.slot < 0 || t.slot >= n_slots)) {
+      t.absent = true;                                           // no resident weights: status 2, nothing computed
+      t.slot = kSlotSkip;
+    }
   }
+  if (t.tok_end <= t.tok_begin) t.slot = kSlotSkip;
   return t;
 }
+
+// Which tile a CTA pair works on in its j-th round.  Mode 0: table order, fixed
+// stride.  Mode 1: chunks ranked by size (`order`), ranked tiles dealt out
+// boustrophedon.  Mode 2: as 1, odd pairs walk their rounds backwards.
+// All roles of both CTAs of a pair evaluate the same function: no hand-off.
+struct Sched {
+  int total, n_pairs, pair, n_wtiles, rounds, mode, n_chunks, group;
+  const uint16_t *order;
+  __device__ __forceinline__ bool tile(int j, int &c, int &wt) const {
+    int t;
+    if (mode == 0) {
+      t = pair + j * n_pairs;
+      if (group > 1) {
+        // Raster blocks of `group` chunks x all weight tiles, chunk index fastest:
+        // the pairs that run at the same time then share weight tiles as well as
+        // token chunks, instead of all reading one or two token chunks.
+        if (t >= total) return false;
+        const int per_block = group * n_wtiles;
+        const int blk = t / per_block, in = t - blk * per_block;
+        const int c0 = blk * group;
+        const int g = min(group, n_chunks - c0);          // the last block may be narrower
+        wt = in / g;
+        c = c0 + (in - wt * g);
+        return true;
+      }
+    } else {
+      const int jj = (mode == 2 && (pair & 1)) ? rounds - 1 - j : j;
+      t = jj * n_pairs + ((jj & 1) ? n_pairs - 1 - pair : pair);
+    }
+    if (t >= total) return false;
+    const int r = t / n_wtiles;
+    wt = t - r * n_wtiles;
+    c = mode == 0 ? r : (int)order[r];
+    return true;
+  }
+};
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -202,23 +260,34 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
                  int32_t *__restrict__ status, int skip_rows_upto, int dense_chunk, int light_max,
-                 const unsigned long long *__restrict__ row_dst) {
+                 const unsigned long long *__restrict__ row_dst, int n_stages, int sched_mode, int dense_group) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_full = smem_base + kStages * kStageBytes;     // kStages  (used in the leader CTA)
+  const uint32_t stage_bytes_all = (uint32_t)n_stages * kStageBytes;
+  const uint32_t bar_full = smem_base + stage_bytes_all;            // kStages  (used in the leader CTA)
   const uint32_t bar_empty = bar_full + 8 * kStages;               // kStages  (both CTAs)
   const uint32_t bar_tfull = bar_empty + 8 * kStages;              // 2        (both CTAs)
   const uint32_t bar_tempty = bar_tfull + 16;                      // 2        (leader CTA)
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_al + kStages * kStageBytes + 8 * (2 * kStages + 4));
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_al + stage_bytes_all + 8 * (2 * kStages + 4));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  unsigned char *scatter_stage = smem_al + stage_bytes_all + 256;
+  uint16_t *order = reinterpret_cast<uint16_t *>(scatter_stage + 2 * kScatterTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();               // 0 = leader
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
   const int n_chunks = tile_table ? __ldg(tile_table) : (dense_rows + dense_chunk - 1) / dense_chunk;
-  const int total = n_chunks * n_wtiles;
+  Sched sch;
+  sch.pair = blockIdx.x >> 1;
+  sch.n_pairs = gridDim.x >> 1;
+  sch.n_wtiles = n_wtiles;
+  sch.total = n_chunks * n_wtiles;
+  sch.rounds = (sch.total + sch.n_pairs - 1) / sch.n_pairs;
+  sch.mode = (tile_table != nullptr && n_chunks <= kMaxSched) ? sched_mode : 0;
+  sch.n_chunks = n_chunks;
+  sch.group = tile_table == nullptr ? dense_group : 1;
+  sch.order = order;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
@@ -232,6 +301,26 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                  ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
+  if (sch.mode != 0) {
+    // Rank the chunks by padded row count, largest first, ties in table order.
+    // Every CTA computes the same ranking; the keys sit in the scatter staging
+    // area, which no epilogue warp touches before the barrier below.
+    uint16_t *keys = reinterpret_cast<uint16_t *>(scatter_stage);
+    for (int i = threadIdx.x; i < n_chunks; i += kThreads) {
+      const int4 e = __ldg(reinterpret_cast<const int4 *>(tile_table + kTileHeaderInts) + i);
+      keys[i] = (uint16_t)min(max(e.z - e.y + 15, 0) >> 4, 65535);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_chunks; i += kThreads) {
+      const uint16_t k = keys[i];
+      int rank = 0;
+      for (int j = 0; j < n_chunks; ++j) {
+        const uint16_t kj = keys[j];
+        rank += (kj > k || (kj == k && j < i)) ? 1 : 0;
+      }
+      order[rank] = (uint16_t)i;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();            // the peer's barriers exist before anything signals them
@@ -243,14 +332,12 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < total; tile += n_pairs) {
-        const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-        Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk);
+      for (int j = 0; ok && j < sch.rounds; ++j) {
+        int c, wt;
+        if (!sch.tile(j, c, wt)) continue;
+        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk, n_slots);
+        if (ch.absent && cta == 0 && wt == 0 && status) atomicExch(status, 2);
         if (ch.slot == kSlotSkip) continue;
-        if (ch.slot < 0 || ch.slot >= n_slots) {
-          if (status) atomicExch(status, 2);
-          ch.slot = 0;
-        }
         const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
         const int tok0 = ch.tok_begin + (int)cta * (n >> 1);       // this CTA's half of the tokens
         const int wrow = wt * kTileW + (int)cta * kRowsPerCta;
@@ -266,12 +353,12 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           const uint32_t sa = smem_base + stage * kStageBytes;
           const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
           if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * steps * (kABytes + tok_bytes));
-          for (int j = 0; j < steps; ++j)
-            tma_pair_load_3d(sa + j * kABytes, &tm_w, full_leader, (kb + j) * kBlockK, wrow, ch.slot);
-          for (int j = 0; j < steps; ++j)
-            tma_pair_load_2d(light ? sa + 2 * kABytes + j * kLightTokBytes : sa + kABytes, tok_map, full_leader,
-                             (kb + j) * kBlockK, tok0);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          for (int q = 0; q < steps; ++q)
+            tma_pair_load_3d(sa + q * kABytes, &tm_w, full_leader, (kb + q) * kBlockK, wrow, ch.slot);
+          for (int q = 0; q < steps; ++q)
+            tma_pair_load_2d(light ? sa + 2 * kABytes + q * kLightTokBytes : sa + kABytes, tok_map, full_leader,
+                             (kb + q) * kBlockK, tok0);
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -281,8 +368,10 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < total; tile += n_pairs) {
-        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, tile / n_wtiles, skip_rows_upto, dense_chunk);
+      for (int j = 0; ok && j < sch.rounds; ++j) {
+        int c, wt;
+        if (!sch.tile(j, c, wt)) continue;
+        const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk, n_slots);
         if (ch.slot == kSlotSkip) continue;
         const int n = ((ch.tok_end - ch.tok_begin) + 15) & ~15;
         const uint32_t idesc = idesc_m256(n);
@@ -295,16 +384,16 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           tc_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes;
           const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
-          for (int j = 0; j < steps; ++j) {
-            const uint64_t adesc = umma_desc_sw128(sa + j * kABytes);
-            const uint64_t bdesc = umma_desc_sw128(light ? sa + 2 * kABytes + j * kLightTokBytes : sa + kABytes);
+          for (int q = 0; q < steps; ++q) {
+            const uint64_t adesc = umma_desc_sw128(sa + q * kABytes);
+            const uint64_t bdesc = umma_desc_sw128(light ? sa + 2 * kABytes + q * kLightTokBytes : sa + kABytes);
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k)
               tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                               (kb | j | k) != 0 ? 1u : 0u);
+                               (kb | q | k) != 0 ? 1u : 0u);
           }
           tc_commit_pair(bar_empty + 8 * stage);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         tc_commit_pair(bar_tfull + 8 * acc);
@@ -321,11 +410,25 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     const int wl = lane_group * 32 + lane;              // weight row inside this CTA's 128
     const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
     int acc = 0; uint32_t acc_phase = 0;
-    for (int tile = pair; tile < total; tile += n_pairs) {
-      const int c = tile / n_wtiles, wt = tile - c * n_wtiles;
-      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk);
+    for (int j = 0; j < sch.rounds; ++j) {
+      int c, wt;
+      if (!sch.tile(j, c, wt)) continue;
+      const Chunk ch = read_chunk(tile_table, dense_rows, slot_of_expert, c, skip_rows_upto, dense_chunk, n_slots);
       if (ch.slot == kSlotSkip) continue;
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      bool ready = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag);
+      if (MODE == kModeScale && row_dst != nullptr) {
+        // The four warps of a half meet at named barriers while they stage rows:
+        // they go on together or leave together, whichever warp saw the abort.
+        uint32_t all_ready;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, %2, %3, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(all_ready) : "r"((uint32_t)ready), "r"(1 + half), "r"(128) : "memory");
+        ready = all_ready != 0;
+      }
+      if (!ready) break;
       tc_fence_after();
       const int n_tok = ch.tok_end - ch.tok_begin;
       const uint32_t taddr = tmem_base + (uint32_t)acc * kMaxN + ((uint32_t)(lane_group * 32) << 16);
@@ -369,10 +472,10 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (row_dst == nullptr) {
             __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float sc = __shfl_sync(0xffffffffu, my_scale, j);
-              const float y = round_bf16(__uint_as_float(v[j])) * sc;
-              if (col_ok && c0 + j < n_tok) obase[(size_t)j * ld_out] = __float2bfloat16_rn(y);
+            for (int q = 0; q < 32; ++q) {
+              const float sc = __shfl_sync(0xffffffffu, my_scale, q);
+              const float y = round_bf16(__uint_as_float(v[q])) * sc;
+              if (col_ok && c0 + q < n_tok) obase[(size_t)q * ld_out] = __float2bfloat16_rn(y);
             }
           } else {
             // Scatter: every row goes straight to the address its sender asked for
@@ -383,16 +486,15 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // 256-byte row segments, not 64-byte ones.
             unsigned long long my_dst = 0ull;
             if (c0 + lane < n_tok) my_dst = row_dst[ch.tok_begin + c0 + lane];
-            __nv_bfloat16 *stg = reinterpret_cast<__nv_bfloat16 *>(
-                smem_al + kStages * kStageBytes + 256 + half * kScatterTileBytes);
+            __nv_bfloat16 *stg = reinterpret_cast<__nv_bfloat16 *>(scatter_stage + half * kScatterTileBytes);
             const int col0 = wt * kTileW + (int)cta * kRowsPerCta;       // first output column of this CTA
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float sc = __shfl_sync(0xffffffffu, my_scale, sub * 16 + j);
-                const float y = round_bf16(__uint_as_float(v[sub * 16 + j])) * sc;
-                stg[j * kRowsPerCta + wl] = __float2bfloat16_rn(y);
+              for (int q = 0; q < 16; ++q) {
+                const float sc = __shfl_sync(0xffffffffu, my_scale, sub * 16 + q);
+                const float y = round_bf16(__uint_as_float(v[sub * 16 + q])) * sc;
+                stg[q * kRowsPerCta + wl] = __float2bfloat16_rn(y);
               }
               asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
 #pragma unroll
@@ -433,6 +535,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   }
 }
 
+// Tuning knobs behind sb_set_tuning (process-wide, read at launch time).
+std::atomic<int> g_sched_mode{1};      // 0 table order / fixed stride, 1 ranked boustrophedon, 2 odd pairs backwards
+std::atomic<int> g_dense_group{1};     // dense passes: row chunks per raster block (1 = chunk-major walk)
+int sched_mode() { return g_sched_mode.load(std::memory_order_relaxed); }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -451,8 +558,8 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what,
-                 uint32_t box_rows = kRowsPerCta) {
+int32_t encode_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what,
+                   uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(SB_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -468,32 +575,117 @@ int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, ui
   return SB_OK;
 }
 
+// A tensor map depends only on (base, extents, box): a serving loop calls with
+// the same few buffers every step, so each host thread remembers the last maps
+// it encoded instead of asking the driver seven times per call.  The map holds
+// no reference to the memory; a reused address with the same extents gives the
+// same bytes.
+struct MapKey {
+  const void *base; uint64_t d0, d1, d2; uint32_t box_rows;
+  bool operator==(const MapKey &o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && box_rows == o.box_rows;
+  }
+};
+constexpr int kMapCacheSize = 64;
+struct MapCache {
+  MapKey key[kMapCacheSize];
+  CUtensorMap map[kMapCacheSize];
+  int used = 0, next = 0;
+};
+
+int32_t make_map(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, const char *what,
+                 uint32_t box_rows = kRowsPerCta) {
+  static thread_local MapCache cache;
+  const MapKey k = {base, d0, d1, d2, box_rows};
+  for (int i = 0; i < cache.used; ++i)
+    if (cache.key[i] == k) { *tm = cache.map[i]; return SB_OK; }
+  int32_t rc = encode_map(tm, base, d0, d1, d2, what, box_rows);
+  if (rc != SB_OK) return rc;
+  const int slot = cache.used < kMapCacheSize ? cache.used++ : (cache.next++ % kMapCacheSize);
+  cache.key[slot] = k;
+  cache.map[slot] = *tm;
+  return SB_OK;
+}
+
+// Shared-memory opt-in and carve-out preference of both kernel instances, once
+// per device (the attributes are per device and per function).
+int32_t prepare_device() {
+  static std::mutex mu;
+  static bool done[64];
+  int dev = -1;
+  SB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SB_E_CUDA, "sb_grouped_swiglu: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (done[dev]) return SB_OK;
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes(kStages)));
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeScale>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes(kStages)));
+  // the largest shared-memory split, so that small kernels of other streams
+  // (router, sort, gather) can share an SM with a resident GEMM CTA
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeSwiglu>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeScale>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
+  done[dev] = true;
+  return SB_OK;
+}
+
+// Rows per chunk of a dense (single-slot) pass: the multiple of 16 in [192, 256]
+// that gives the cheapest schedule over `pairs` CTA pairs, a tile of c rows
+// costing c + 256 (its MMA time grows with c, the weight tile it streams does
+// not).  4096 rows x 8 weight tiles on 74 pairs: chunks of 256 make 128 tiles =
+// two rounds of 256-row tiles; chunks of 240 make 144 tiles = two rounds of
+// 240-row tiles.
+int dense_chunk_rows(int rows, int n_wtiles, int pairs) {
+  int best = kMaxN;
+  long best_cost = -1;
+  for (int c = kMaxN; c >= 192; c -= 16) {
+    const long full = rows / c, rest = rows - full * c;
+    const long rounds_full = (full * n_wtiles + pairs - 1) / pairs;
+    // the remainder chunk's tiles ride along in the last round if it has room, else they add a short round
+    const long spare = rounds_full * pairs - full * n_wtiles;
+    const long cost = rounds_full * (c + 256) + ((rest > 0 && spare < n_wtiles) ? (((rest + 15) & ~15L) + 256) : 0);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
+  }
+  return best;
+}
+
 template <int MODE>
 int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
                     int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto,
-                    const unsigned long long *row_dst, cudaStream_t stream) {
-  // Dense rows are cut into chunks of kMaxN tokens.  (Smaller chunks give more
-  // tiles for a small batch but were slower on B200: every chunk re-streams the
-  // whole weight tile from L2.)
-  const int dense_chunk = kMaxN;
+                    const unsigned long long *row_dst, int n_stages, cudaStream_t stream) {
+  const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
+  const int dense_chunk = tile_table == nullptr ? dense_chunk_rows(dense_rows, n_wtiles, grid / 2) : kMaxN;
   const int probe_light = 16;
   auto kern = pair_gemm_kernel<MODE>;
-  SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-  // ask for the largest shared-memory split so that small kernels of other
-  // streams (router, sort, gather) can share an SM with a resident GEMM CTA
-  SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     (int)cudaSharedmemCarveoutMaxShared));
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
-                                              slot_of_expert,
-                                              static_cast<const __nv_bfloat16 *>(row_scale),
-                                              static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb, n_slots,
-                                              status, skip_rows_upto, dense_chunk, probe_light, row_dst);
+  kern<<<grid, kThreads, smem_bytes(n_stages), stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
+                                                        slot_of_expert,
+                                                        static_cast<const __nv_bfloat16 *>(row_scale),
+                                                        static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb,
+                                                        n_slots, status, skip_rows_upto, dense_chunk, probe_light,
+                                                        row_dst, n_stages, sched_mode(),
+                                                        g_dense_group.load(std::memory_order_relaxed));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
 
 }  // namespace
+
+int32_t set_gemm_tuning(const char *key, int value) {
+  if (strcmp(key, "sched") == 0) {
+    if (value < 0 || value > 2) return fail(SB_E_INVALID_ARG, "sb_set_tuning: sched must be 0, 1 or 2");
+    g_sched_mode.store(value);
+    return SB_OK;
+  }
+  if (strcmp(key, "dense_group") == 0) {
+    if (value < 1 || value > 64) return fail(SB_E_INVALID_ARG, "sb_set_tuning: dense_group must be in [1,64]");
+    g_dense_group.store(value);
+    return SB_OK;
+  }
+  return SB_E_UNSUPPORTED;      // not a GEMM key
+}
 
 // w13 must be in the INTERLEAVED row order (row 2j = gate_j, row 2j+1 = up_j);
 // tile_table must have been built with 256-row tiles.  Tile entries of at most
@@ -501,12 +693,13 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
 // limits the grid to that many CTA pairs.  With `row_dst` (one device address per
 // row, 0 = drop) the down pass writes each result row to that address instead
 // of `out`.  `passes`: 1 = gate/up + SwiGLU only, 2 = down only (hbuf already
-// holds the intermediate rows), 3 = both.
+// holds the intermediate rows), 3 = both.  `stages` in [2, 6] is the depth of
+// the shared-memory pipeline (0 = 6); 5 leaves room on the SM for a router CTA.
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
                                    int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
-                                   cudaStream_t stream, int passes) {
+                                   cudaStream_t stream, int passes, int stages) {
   if (H < kBlockK || I < kBlockK || H % kBlockK != 0 || I % kBlockK != 0)
     return fail(SB_E_UNSUPPORTED, "sb_grouped_swiglu: H and I must be multiples of %d (H=%d I=%d)", kBlockK, H, I);
   if (R_cap <= 0 || S < 1) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: R_cap=%d S=%d", R_cap, S);
@@ -516,26 +709,29 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (!rows || !w13 || !w2 || !hbuf || (!out && !row_dst)) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
   if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || (out && !aligned(out, 16)))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
+  if (stages == 0) stages = kStages;
+  if (stages < 2 || stages > kStages) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: stages=%d outside [2,%d]", stages, kStages);
+  int32_t rc = prepare_device();
+  if (rc != SB_OK) return rc;
   CUtensorMap tm_x[3], tm_w13, tm_h[3], tm_w2;
   const uint32_t boxes[3] = {128, 64, 16};
-  int32_t rc;
   for (int b = 0; b < 3; ++b) {
-    if ((rc = make_map(&tm_x[b], rows, (uint64_t)H, (uint64_t)R_cap, 0, "rows", boxes[b])) != SB_OK) return rc;
-    if ((rc = make_map(&tm_h[b], hbuf, (uint64_t)I, (uint64_t)R_cap, 0, "hbuf", boxes[b])) != SB_OK) return rc;
+    if ((passes & 1) && (rc = make_map(&tm_x[b], rows, (uint64_t)H, (uint64_t)R_cap, 0, "rows", boxes[b])) != SB_OK) return rc;
+    if ((passes & 2) && (rc = make_map(&tm_h[b], hbuf, (uint64_t)I, (uint64_t)R_cap, 0, "hbuf", boxes[b])) != SB_OK) return rc;
   }
-  if ((rc = make_map(&tm_w13, w13, (uint64_t)H, (uint64_t)2 * I, (uint64_t)S, "w13")) != SB_OK) return rc;
-  if ((rc = make_map(&tm_w2, w2, (uint64_t)I, (uint64_t)H, (uint64_t)S, "w2")) != SB_OK) return rc;
+  if ((passes & 1) && (rc = make_map(&tm_w13, w13, (uint64_t)H, (uint64_t)2 * I, (uint64_t)S, "w13")) != SB_OK) return rc;
+  if ((passes & 2) && (rc = make_map(&tm_w2, w2, (uint64_t)I, (uint64_t)H, (uint64_t)S, "w2")) != SB_OK) return rc;
   int grid = (sb_device_sm_count() / 2) * 2;
   if (grid <= 0) return fail(SB_E_CUDA, "sb_grouped_swiglu: no CUDA device");
   if (max_pairs > 0 && 2 * max_pairs < grid) grid = 2 * max_pairs;     // leave the other SMs to a concurrent launch
   if (passes & 1) {
     rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
-                                  H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stream);
+                                  H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stages, stream);
     if (rc != SB_OK) return rc;
   }
   if (!(passes & 2)) return SB_OK;
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
-                                 I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stream);
+                                 I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stages, stream);
 }
 
 }  // namespace sb

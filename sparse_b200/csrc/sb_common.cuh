@@ -101,15 +101,13 @@ int32_t launch_permute(const void *x, const int32_t *item_expert, const void *it
                        size_t ws_bytes, void *out_rows, int32_t *expert_offsets,
                        int32_t *slot_of_item, int32_t *item_of_slot, void *slot_scale,
                        int32_t *tile_table, cudaStream_t stream);
-int32_t launch_grouped_swiglu(const void *rows, const int32_t *tile_table, int dense_rows,
-                              const void *w13, const void *w2, const int32_t *slot_of_expert,
-                              const void *row_scale, int R_cap, int H, int I, int S,
-                              void *hbuf, void *out, int32_t *status, cudaStream_t stream);
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows,
                                    const void *w13, const void *w2, const int32_t *slot_of_expert,
                                    const void *row_scale, int R_cap, int H, int I, int S,
-                                   void *hbuf, void *out, int32_t *status, int skip_rows_upto, int max_pairs, const unsigned long long *row_dst,
-                                   cudaStream_t stream, int passes = 3);
+                                   void *hbuf, void *out, int32_t *status, int skip_rows_upto, int max_pairs,
+                                   const unsigned long long *row_dst, cudaStream_t stream, int passes = 3,
+                                   int stages = 0);
+int32_t set_gemm_tuning(const char *key, int value);
 int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int items_per_row,
                               const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,

@@ -174,7 +174,7 @@ class EpRank:
 
     def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int, rank: int, ep: int,
                  owner: Sequence[int], bufs: PeerBuffers, renorm: bool = False,
-                 fp32_logits: bool = False):
+                 fp32_logits: bool = False, owner_decode: Optional[Sequence[int]] = None):
         self.w, self.top_k, self.rank, self.ep = weights, top_k, rank, ep
         self.renorm, self.fp32_logits = renorm, fp32_logits
         self.bufs = bufs
@@ -184,8 +184,15 @@ class EpRank:
         self.max_tokens = max_tokens
         n = max_tokens * top_k
         i32, bf = torch.int32, torch.bfloat16
-        self.owner = owner_table(owner, ep, e).to(dev)              # [ep][E]
-        self.owner_row = self.owner[rank]                            # this rank's destinations
+        # Destination tables [ep][E], one per stage: the reference picks the table
+        # of the current stage on every forward (utils/eval_core.py:6736-6769) and
+        # its launchers keep decode on round-robin while prefill follows the
+        # placement (SPARSE_SCP_APPLY_DECODE=0).  `use_stage` switches between them.
+        pre = owner_table(owner, ep, e).to(dev)
+        dec = pre if owner_decode is None else owner_table(owner_decode, ep, e).to(dev)
+        self._owners = {"prefill": (pre, pre[rank].contiguous()), "decode": (dec, dec[rank].contiguous())}
+        self.stage = "prefill"
+        self.owner, self.owner_row = self._owners["prefill"]        # [ep][E]; this rank's destinations
         self.topk_idx = torch.empty((max_tokens, top_k), dtype=i32, device=dev)
         self.topk_w = torch.empty((max_tokens, top_k), dtype=bf, device=dev)
         self.logits = torch.empty((max_tokens, e), dtype=torch.float32 if fp32_logits else bf, device=dev)
@@ -220,9 +227,16 @@ class EpRank:
         # read the owners' output buffers after the GEMM.
         self.scatter_return = bool(lib.sb_w13_interleaved())
         self.row_dst = torch.zeros((bufs.recv_cap,), dtype=torch.int64, device=dev)
-        self.identity = torch.arange(max(n, 1), dtype=i32, device=dev)
         self.route_ws = torch.empty((_lib.DECODE_MAX_TOKENS * e,), dtype=torch.float32, device=dev)
         self.local_scale = torch.empty((max(_lib.DECODE_MAX_TOKENS * top_k, 1),), dtype=bf, device=dev)
+
+    def use_stage(self, stage: str) -> None:
+        """Route this and the following passes by the destination table of `stage`
+        ("prefill" or "decode"); every rank must switch at the same pass."""
+        if stage not in self._owners:
+            raise ValueError("stage must be prefill or decode, got %r" % (stage,))
+        self.stage = stage
+        self.owner, self.owner_row = self._owners[stage]
 
     def _s(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
@@ -231,11 +245,16 @@ class EpRank:
         return self.small_batch_kernels and 0 < self._t <= _lib.DECODE_MAX_TOKENS
 
     # -- stages -------------------------------------------------------------------
-    def stage_route(self, x: torch.Tensor) -> None:
-        w, t, k = self.w, x.shape[0], self.top_k
-        if t > self.max_tokens:
-            raise RuntimeError("EP layer was sized for %d tokens, got %d" % (self.max_tokens, t))
-        self._x, self._t = x, t
+    def begin(self, x: torch.Tensor) -> None:
+        """Names the batch of this pass (every stage below works on it)."""
+        if x.shape[0] > self.max_tokens:
+            raise RuntimeError("EP layer was sized for %d tokens, got %d" % (self.max_tokens, x.shape[0]))
+        self._x, self._t = x, x.shape[0]
+
+    def stage_route(self, x: Optional[torch.Tensor] = None) -> None:
+        if x is not None:
+            self.begin(x)
+        w, x, t, k = self.w, self._x, self._t, self.top_k
         if self._small():
             check(lib.sb_route_decode(
                 x.data_ptr(), w.router_w.data_ptr(),
@@ -270,12 +289,28 @@ class EpRank:
               "sb_ep_publish_counts")
         self.launches += 1
 
+    # Wait limit of the cross-rank barriers in nanoseconds (None = the library's 2 s).
+    barrier_limit_ns: Optional[int] = None
+
     def stage_barrier(self) -> None:
         b = self.bufs
-        check(lib.sb_ep_barrier_seq(b.ptr_array("ctl", b.flags_offset), self.rank, self.ep,
-                                    b.local["ctl"] + b.epoch_offset, self.status.data_ptr(), self._s()),
-              "sb_ep_barrier_seq")
+        if self.barrier_limit_ns is None:
+            check(lib.sb_ep_barrier_seq(b.ptr_array("ctl", b.flags_offset), self.rank, self.ep,
+                                        b.local["ctl"] + b.epoch_offset, self.status.data_ptr(), self._s()),
+                  "sb_ep_barrier_seq")
+        else:
+            check(lib.sb_ep_barrier_timed(b.ptr_array("ctl", b.flags_offset), self.rank, self.ep,
+                                          b.local["ctl"] + b.epoch_offset, int(self.barrier_limit_ns),
+                                          self.status.data_ptr(), self._s()), "sb_ep_barrier_timed")
         self.launches += 1
+
+    def check_status(self) -> None:
+        """Host-synchronising read of the device status word; raises on a non-zero value."""
+        s = int(self.status.item())
+        if s != 0:
+            self.status.zero_()
+            raise RuntimeError("sparse_b200 EP device status %d (1: GEMM wait expired, 2: expert "
+                               "without a weight slot, 3: peer barrier wait expired)" % s)
 
     def stage_exchange_dispatch(self) -> None:
         """publish + barrier + plan + dispatch + barrier as one launch (decode-sized steps)."""
@@ -294,13 +329,18 @@ class EpRank:
         self._scattered = self.scatter_return
 
     def stage_experts_and_shared(self) -> None:
-        """Routed groups and the shared expert in one pair of weight-streaming launches."""
+        """Routed groups and the shared expert in one pair of weight-streaming launches.
+
+        The row bound handed to the library is the whole receive buffer: the
+        streaming kernels sweep a group of any size 16 rows at a time, so a peer
+        that sends a prefill-sized batch in the same step (ranks may mix the two
+        branches) gets every row computed, only slower than the tile kernel would."""
         w, b, t = self.w, self.bufs, self._t
         has_shared = bool(w.shared_inter) and t > 0
         check(lib.sb_grouped_swiglu_mixed(
             b.local["rows"], self.recv_tiles.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(),
             w.slot_of_expert.data_ptr(), b.local["scale"], b.recv_cap, w.hidden, w.inter, w.n_slots,
-            self.hbuf.data_ptr(), b.local["y"], self.ep * _lib.DECODE_MAX_TOKENS,
+            self.hbuf.data_ptr(), b.local["y"], b.recv_cap,
             self._x.data_ptr() if has_shared else None,
             w.shared_w13.data_ptr() if has_shared else None, w.shared_w2.data_ptr() if has_shared else None,
             self.shared_scale.data_ptr() if has_shared and w.shared_gate_w is not None else None,
@@ -329,9 +369,10 @@ class EpRank:
         self.launches += 1
         self._scattered = self.scatter_return
 
-    def stage_shared(self, passes: int = 3) -> None:
+    def stage_shared(self, passes: int = 3, stages: int = 0) -> None:
         """The shared expert on this rank's own tokens; `passes` 1 / 2 run only its
-        gate/up or only its down pass (batches above the decode size)."""
+        gate/up or only its down pass (batches above the decode size), `stages`
+        is the GEMM's pipeline depth (5 leaves room for a router CTA on each SM)."""
         w, t = self.w, self._t
         if not w.shared_inter or t == 0:
             return
@@ -339,7 +380,7 @@ class EpRank:
             check(lib.sb_grouped_swiglu_passes(
                 self._x.data_ptr(), None, t, w.shared_w13.data_ptr(), w.shared_w2.data_ptr(), None,
                 self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, t, w.hidden,
-                w.shared_inter, 1, self.shared_h.data_ptr(), self.shared_out.data_ptr(), passes,
+                w.shared_inter, 1, self.shared_h.data_ptr(), self.shared_out.data_ptr(), passes, stages,
                 self.status.data_ptr(), self._s()), "sb_grouped_swiglu_passes(shared)")
             self.launches += 1
             return
@@ -413,8 +454,11 @@ class EpRank:
         w, t, k = self.w, self._t, self.top_k
         dst = self.out[:t] if out is None else out
         if self._scattered:
-            # every row of this rank's items is already here, in item order
-            check(lib.sb_combine(self.bufs.local["ret"], self.identity.data_ptr(), self.topk_idx.data_ptr(),
+            # every row of this rank's items is already here, in item order; with
+            # return addresses the dispatch wrote item_row[i] = i, or -1 for an item
+            # that was never sent (expert id out of range, no room), which the
+            # combine then skips instead of adding a stale row
+            check(lib.sb_combine(self.bufs.local["ret"], self.item_row.data_ptr(), self.topk_idx.data_ptr(),
                                  self.shared_out.data_ptr() if w.shared_inter else None, t, w.hidden, k,
                                  dst.data_ptr(), self._s()), "sb_combine")
             self.launches += 1
@@ -434,7 +478,7 @@ class ExpertParallelLayer:
 
     def __init__(self, weights: LayerWeights, top_k: int, max_tokens: int, rank: int, ep: int,
                  process_group, owner: Optional[Sequence[int]] = None, renorm: bool = False,
-                 fp32_logits: bool = False):
+                 fp32_logits: bool = False, owner_decode: Optional[Sequence[int]] = None):
         if owner is None:
             owner = [e % ep for e in range(weights.num_experts)]
         cap = recv_capacity(max_tokens, top_k, ep)
@@ -447,22 +491,16 @@ class ExpertParallelLayer:
                 exchange_handles(bufs, process_group)
             self._shared_bufs[key] = bufs
         self.bufs = bufs
-        self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits)
+        self.r = EpRank(weights, top_k, max_tokens, rank, ep, owner, bufs, renorm, fp32_logits,
+                        owner_decode=owner_decode)
         self.last_launches = 0
         self.overlap = True
-        # How routed results travel back: "fused" = peer stores from the down GEMM's
-        # epilogue; "split" = whole-row pushes on the side stream beside the shared
-        # expert's down pass.  auto = fused (measured 3-6 % faster than split on 2 and 8 GPUs).
-        mode = os.environ.get("SPARSE_B200_EP_RETURN", "auto")
-        if mode not in ("auto", "fused", "split"):
-            raise ValueError("SPARSE_B200_EP_RETURN must be auto, fused or split")
-        self.return_mode = mode if mode != "auto" else "fused"
         with torch.cuda.device(weights.device):
             self._side = torch.cuda.Stream(device=weights.device)
             self._fork = torch.cuda.Event()
+            self._mid = torch.cuda.Event()
             self._join = torch.cuda.Event()
-            self._fork2 = torch.cuda.Event()
-            self._join2 = torch.cuda.Event()
+        self._graphs = {}
 
     @property
     def logits(self):
@@ -479,8 +517,13 @@ class ExpertParallelLayer:
     def _barrier(self) -> None:
         self.r.stage_barrier()
 
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                stage: Optional[str] = None) -> torch.Tensor:
+        """One layer pass; `stage` ("prefill" / "decode") picks the destination
+        table, None keeps the one in use."""
         r = self.r
+        if stage is not None and stage != r.stage:
+            r.use_stage(stage)
         r.launches = 0
         marks = self.stage_events
         stream = torch.cuda.current_stream(r.device)
@@ -521,37 +564,33 @@ class ExpertParallelLayer:
                 self.last_launches = r.launches
                 return res
             else:
-                # The shared expert needs nothing from the peers, so its two passes
-                # cover the two transfers: gate/up runs while counts, plan, dispatch
-                # and the "rows landed" barrier run on the side stream; down runs
-                # while the routed results travel back to their senders.
-                r.stage_route(x)
-                r.stage_publish()
+                # The shared expert's gate/up pass needs nothing from the routing
+                # and its down pass only the scalar gate, so the whole send side
+                # runs beside it on the side stream: router, sort, counts, plan,
+                # dispatch and the "rows landed" barrier.  The gate/up launch goes
+                # first with a pipeline one stage short, which leaves each SM room
+                # for one router CTA: the router's CUDA-core dot products run under
+                # the tensor-core pass, not in front of it.
+                r.begin(x)
+                has_shared = bool(r.w.shared_inter)
                 self._fork.record(stream)
+                if has_shared:
+                    r.stage_shared(1, stages=5)
                 with torch.cuda.stream(self._side):
                     self._side.wait_event(self._fork)
+                    r.stage_route()
+                    self._mid.record(self._side)
+                    r.stage_publish()
                     self._barrier()
                     r.stage_plan()
                     r.stage_dispatch()
                     self._barrier()
                     r.stage_resolve()
                     self._join.record(self._side)
-                split = r._scattered and not r._small() and self.return_mode == "split"
-                r.stage_shared(1 if split else 3)
-                stream.wait_event(self._join)
-                if split:
-                    r.stage_experts(fused=False)
-                    self._fork2.record(stream)
-                    with torch.cuda.stream(self._side):
-                        self._side.wait_event(self._fork2)
-                        r.stage_return()
-                        self._barrier()
-                        self._join2.record(self._side)
+                stream.wait_event(self._mid)            # the scalar gate of the shared expert is known
+                if has_shared:
                     r.stage_shared(2)
-                    stream.wait_event(self._join2)
-                    res = r.stage_combine(out)
-                    self.last_launches = r.launches
-                    return res
+                stream.wait_event(self._join)
             fused = marks is None          # the timing marks time the GEMM and the return push separately
             r.stage_experts(fused=fused)
             mark("routed_swiglu")
@@ -565,15 +604,43 @@ class ExpertParallelLayer:
         self.last_launches = r.launches
         return res
 
+    def forward_graphed(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        stage: Optional[str] = None) -> torch.Tensor:
+        """`forward` replayed from a CUDA graph: the first call with a given input
+        and output buffer records the step's launches (two streams, device-side
+        barrier epochs, nothing baked in that changes from step to step), later
+        calls cost the host one graph launch instead of some twenty kernel
+        launches.  Recording executes nothing, so every rank must make the same
+        sequence of calls (as with `forward`); call `forward` once before the first
+        recording so that one-time set-up is not captured."""
+        r = self.r
+        if stage is not None and stage != r.stage:
+            r.use_stage(stage)
+        dst = r.out[:x.shape[0]] if out is None else out
+        key = (x.data_ptr(), x.shape[0], dst.data_ptr(), r.stage)
+        ent = self._graphs.get(key)
+        if ent is None:
+            if len(self._graphs) >= 32:
+                self._graphs.clear()
+            stream = torch.cuda.current_stream(r.device)
+            cap = torch.cuda.Stream(device=r.device)
+            cap.wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(cap):
+                with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
+                    self.forward(x, dst)
+            stream.wait_stream(cap)
+            ent = (graph, self.last_launches, x, dst)       # keeps the buffers alive
+            self._graphs[key] = ent
+        ent[0].replay()
+        self.last_launches = ent[1]
+        return ent[3]
+
     # When set to a list, forward() appends (stage name, CUDA event) marks to it.
     stage_events = None
 
     def check_status(self) -> None:
-        s = int(self.r.status.item())
-        if s != 0:
-            self.r.status.zero_()
-            raise RuntimeError("sparse_b200 EP device status %d (1: GEMM wait expired, 2: expert "
-                               "without a weight slot, 3: peer barrier wait expired)" % s)
+        self.r.check_status()
 
 
 class CachedExpertParallelLayer(ExpertParallelLayer):
@@ -587,9 +654,9 @@ class CachedExpertParallelLayer(ExpertParallelLayer):
     readiness order when that is enabled.  One stream, stage after stage."""
 
     def __init__(self, cached_runner, top_k: int, max_tokens: int, rank: int, ep: int, process_group,
-                 owner=None, renorm: bool = False, fp32_logits: bool = False):
+                 owner=None, renorm: bool = False, fp32_logits: bool = False, owner_decode=None):
         super().__init__(cached_runner.store.w, top_k, max_tokens, rank, ep, process_group, owner=owner,
-                         renorm=renorm, fp32_logits=fp32_logits)
+                         renorm=renorm, fp32_logits=fp32_logits, owner_decode=owner_decode)
         self.cached = cached_runner
         self.r.status = cached_runner.status          # one status word for both
         self.overlap = False
@@ -600,6 +667,8 @@ class CachedExpertParallelLayer(ExpertParallelLayer):
         r.launches = 0
         t = x.shape[0]
         stage = stage or SparseContext.stage(1 if t == 1 else t)
+        if stage in r._owners and stage != r.stage:
+            r.use_stage(stage)
         with torch.cuda.device(r.device):
             r.stage_route(x)
             r.stage_publish()

@@ -113,6 +113,8 @@ class LayerRunner:
         self.want_logits = want_logits
         self.max_tokens = 0
         self.status = torch.zeros((1,), dtype=torch.int32, device=weights.device)
+        dev_index = weights.device.index if weights.device.index is not None else torch.cuda.current_device()
+        _lib.init_device(dev_index)
         self._reserve(max_tokens)
 
     def _reserve(self, tokens: int) -> None:

@@ -37,13 +37,19 @@ def looks_like_sparse_moe_block(mlp: nn.Module) -> bool:
             or hasattr(mlp, "shared_experts"))
 
 
-def _expert_matrices(experts, e: int, inter_hint: int = 0):
-    """(gate [I,H], up [I,H], down [H,I]) of expert e from either weight layout."""
+def _expert_matrices(experts, e: int):
+    """(gate [I,H], up [I,H], down [H,I]) of expert e from either weight layout:
+    a ModuleList of gate_proj/up_proj/down_proj modules, or fused 3-D parameters
+    gate_up_proj [E,2I,H] (the I gate rows first) and down_proj [E,H,I], which is
+    how the reference applies them (F.linear(x, gate_up_proj[e]) then chunk(2),
+    utils/eval_core.py:11714-11724)."""
     if all(hasattr(experts, a) for a in ("gate_up_proj", "down_proj")):
         gu = experts.gate_up_proj[e]
         dn = experts.down_proj[e]
-        if gu.shape[0] < gu.shape[1] and dn.shape[0] > dn.shape[1]:      # stored [H, 2I] / [I, H]
-            gu, dn = gu.t(), dn.t()
+        if gu.dim() != 2 or dn.dim() != 2 or gu.shape[0] % 2 != 0 or \
+                gu.shape[1] != dn.shape[0] or dn.shape[1] * 2 != gu.shape[0]:
+            raise ValueError("fused expert weights must be gate_up_proj [E,2I,H] and down_proj [E,H,I]; got %s and %s"
+                             % (tuple(experts.gate_up_proj.shape), tuple(experts.down_proj.shape)))
         i = gu.shape[0] // 2
         return gu[:i], gu[i:], dn
     m = list(experts)[e]
@@ -136,9 +142,10 @@ class DistributedSparseMoeBlock(nn.Module):
             self._cache = self.store.cache
             if self.comm_world > 1:
                 from .ep import CachedExpertParallelLayer
-                table = self.placement.dest_table(self.layer_idx, "prefill")
                 self._ep = CachedExpertParallelLayer(self._cached, top_k, max_tokens, self.comm_rank,
-                                                     self.comm_world, process_group, owner=table,
+                                                     self.comm_world, process_group,
+                                                     owner=self.placement.dest_table(self.layer_idx, "prefill"),
+                                                     owner_decode=self.placement.dest_table(self.layer_idx, "decode"),
                                                      renorm=self.norm_topk_prob, fp32_logits=fp32_logits)
         else:
             slot_of = [-1] * num_experts
@@ -150,9 +157,10 @@ class DistributedSparseMoeBlock(nn.Module):
             self._cache = ExpertWeightCache(0)
             if self.comm_world > 1:
                 from .ep import ExpertParallelLayer
-                table = self.placement.dest_table(self.layer_idx, "prefill")
                 self._ep = ExpertParallelLayer(lw, top_k, max_tokens, self.comm_rank, self.comm_world,
-                                               process_group, owner=table,
+                                               process_group,
+                                               owner=self.placement.dest_table(self.layer_idx, "prefill"),
+                                               owner_decode=self.placement.dest_table(self.layer_idx, "decode"),
                                                renorm=self.norm_topk_prob, fp32_logits=fp32_logits)
             else:
                 self._runner = LayerRunner(lw, top_k, max_tokens, renorm=self.norm_topk_prob,
@@ -212,7 +220,7 @@ class DistributedSparseMoeBlock(nn.Module):
         stage = SparseContext.stage(s)
         self._compute_and_schedule_next_layer_rs(x, s)
         if self._ep is not None:
-            out = (self._ep.forward(x, stage=stage) if self._cached is not None else self._ep.forward(x)).clone()
+            out = self._ep.forward(x, stage=stage).clone()
             logits = self._ep.logits[:x.shape[0]]
         elif self._cached is not None:
             out, idx, wts, logits = self._cached.forward(x, stage)

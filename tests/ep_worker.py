@@ -119,6 +119,37 @@ def main():
             blk.check_status()
             assert torch.equal(out_static, wants[it]), "graph-replayed EP rows differ on rank %d" % rank
         dist.barrier()
+        # One step in which the ranks take different branches: rank 0 sends a
+        # decode-sized batch, the others a prefill-sized one, so the decode-sized
+        # rank receives expert groups far above 16 rows.  Eagerly and replayed.
+        t_mix = 8 if rank == 0 else 97
+        ref_mix = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, 128)
+        xm = [synth.make_hidden(t_mix, shape.hidden, seed=1300 + 10 * it + rank).to(torch.bfloat16).to(dev)
+              for it in range(2)]
+        want_mix = [ref_mix.forward(x)[0].clone() for x in xm]
+        for it in range(2):
+            out = blk.forward_device(xm[it]).clone()
+            torch.cuda.synchronize()
+            blk.check_status()
+            assert torch.equal(out, want_mix[it]), "mixed-branch EP rows differ on rank %d" % rank
+        dist.barrier()
+        blk.use_graphs = True
+        for it in range(4):          # first use of each buffer records, later ones replay
+            out = blk.forward_device(xm[it % 2]).clone()
+            torch.cuda.synchronize()
+            blk.check_status()
+            assert torch.equal(out, want_mix[it % 2]), "graph-replayed mixed-branch rows differ on rank %d" % rank
+        # the prefill-sized step through the block's own graph cache
+        xg = [synth.make_hidden(tokens, shape.hidden, seed=1500 + 10 * it + rank).to(torch.bfloat16).to(dev)
+              for it in range(2)]
+        want_g = [ref.forward(x)[0].clone() for x in xg]
+        for it in range(6):
+            out = blk.forward_device(xg[it % 2]).clone()
+            torch.cuda.synchronize()
+            blk.check_status()
+            assert torch.equal(out, want_g[it % 2]), "graph-replayed EP rows differ on rank %d (pass %d)" % (rank, it)
+        blk.use_graphs = False
+        dist.barrier()
     offloaded_case(rank, world, dev)
     print("EP_WORKER_OK rank %d" % rank, flush=True)
     dist.barrier()

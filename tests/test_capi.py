@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported_and_bound():
         assert hasattr(_lib.lib, n), f"{n} declared in the header but not exported"
         assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
     assert set(_lib.SIGNATURES) == set(names)
-    assert _lib.lib.sb_abi_version() == 1
+    assert _lib.lib.sb_abi_version() == 2
 
 
 def test_size_queries_need_no_device():

@@ -198,3 +198,46 @@ def test_bounded_stager_commits_used_transfers_by_slot_exchange():
         slots = [st.cache.peek(e) for e in st.cache.resident_ids()]
         assert len(set(slots)) == len(slots), "two residents share a slab slot"
         assert st.view is None
+
+
+class _FusedExperts(nn.Module):
+    """Experts as two 3-D parameters, the layout the reference's fused-weight
+    path reads (utils/eval_core.py:11714-11731): gate_up_proj [E, 2I, H] with the
+    I gate rows first, down_proj [E, H, I]."""
+
+    def __init__(self, w):
+        super().__init__()
+        gu = torch.stack([torch.cat([w.gate[e], w.up[e]], dim=0) for e in range(w.shape.num_experts)])
+        dn = torch.stack([w.down[e] for e in range(w.shape.num_experts)])
+        self.gate_up_proj = nn.Parameter(gu, requires_grad=False)
+        self.down_proj = nn.Parameter(dn, requires_grad=False)
+        self.act_fn = nn.SiLU()
+
+
+@pytest.mark.parametrize("offload", ["gpu", "cpu"])
+def test_fused_gate_up_layout_equals_module_list_layout(offload):
+    """The same weights handed over as fused 3-D parameters give the bits of the
+    per-expert module list, resident and offloaded."""
+    from sparse_b200.context import SparseContext
+    w = block_weights("TINY", 1.2)
+    SparseContext.initialize(1, num_experts=w.shape.num_experts)
+    ref = _make_block(w, offload="gpu")
+    from sparse_b200.moe_block import DistributedSparseMoeBlock
+    inner = _Inner(w)
+    inner.experts = _FusedExperts(w)
+    blk = DistributedSparseMoeBlock(
+        layer_idx=0, mlp_block=inner.to(torch.bfloat16), scp_map={}, env=_Env(), num_layers=1,
+        num_experts=w.shape.num_experts, top_k=w.shape.top_k, dtype=torch.bfloat16, expert_offload=offload,
+        expert_cache=3 if offload == "cpu" else 0, routing_mode="router", rs_dir="", rs_require_complete=False,
+        rs_prob_to_logit_eps=1e-6, log_routing_stats=False, planner_mode="none", prefetch_top_m=2,
+        placement_mode="round_robin", max_tokens=256)
+    assert (blk.store is not None) == (offload == "cpu")
+    for step, n in enumerate((1, 7, 130)):
+        SparseContext.begin_runtime_call(step)
+        x = synth.make_hidden(n, w.shape.hidden, seed=2000 + step).to(torch.bfloat16).view(1, n, -1).cuda()
+        want, want_logits = ref(x)
+        got, logits = blk(x)
+        torch.cuda.synchronize()
+        blk.check_status()
+        assert torch.equal(logits, want_logits)
+        assert torch.equal(got, want)

@@ -79,6 +79,11 @@ def test_router_against_reference_golden_indices():
     """From x, against what the reference itself selected (library-order logits):
     every differing row is explained by an exact tie or a 1-ulp logit flip."""
     from sparse_b200 import ops
+    # share of rows whose ordered indices differ from the reference's own CPU run
+    # (measured: 2.51 %, 3.71 %, 0 %), and of rows whose selected SET differs
+    # (1.22 %, 1.95 %, 0 %) -- the set is what changes an output row
+    bounds = {"qwen_bf16_zipf_t4096": (0.026, 0.013), "qwen_bf16_t512": (0.038, 0.020),
+              "qwen_fp32_t512": (0.0, 0.0)}
     for name in ("qwen_bf16_zipf_t4096", "qwen_bf16_t512", "qwen_fp32_t512"):
         g = load_golden(name)
         shape = getattr(synth, g["shape"])
@@ -94,7 +99,9 @@ def test_router_against_reference_golden_indices():
         assert int((differs & ~ties & ~flipped).sum()) == 0
         if dt == torch.bfloat16:
             assert float((logits != g["logits"]).float().mean()) < 5e-3
-        assert float(differs.float().mean()) < 0.12
+        set_differs = (idx.sort(dim=1).values != g["topi"].sort(dim=1).values).any(dim=1)
+        assert float(differs.float().mean()) <= bounds[name][0]
+        assert float(set_differs.float().mean()) <= bounds[name][1]
 
 
 def test_topk_tie_rule_on_given_logits():
@@ -115,14 +122,50 @@ def test_topk_tie_rule_on_given_logits():
     rv, ri = mo.softmax_topk(logits, k, True, torch.bfloat16)
     assert torch.equal(idx2.cpu().long(), ri)
     assert int(_bf16_ulp_diff(wts2.cpu(), rv).max()) <= 1
-    # what the reference's library call returns on this device
+    # What the reference's own call returns on this device
+    # (utils/eval_core.py:9591-9595: softmax in fp32, torch.topk on CUDA).  The
+    # selected SET decides the output row (combine re-sorts by expert id): on
+    # tie-heavy logits "larger probability, then smaller id" must pick exactly
+    # the set the library picks.
     probs = torch.softmax(logits.to(dev()), dim=-1, dtype=torch.float32)
     tv, ti = torch.topk(probs, k, dim=-1)
     same_values = torch.equal(tv.cpu().to(torch.bfloat16).float().sort(dim=1).values,
                               want_v.float().sort(dim=1).values)
     assert same_values, "selected probabilities must agree with torch.topk as multisets"
-    exact = float((ti.cpu() == want_i).all(dim=1).float().mean())
-    print(f"rows identical to torch.topk(cuda) including tie order: {exact:.4f}")
+    assert torch.equal(ti.cpu().sort(dim=1).values, idx.cpu().long().sort(dim=1).values), \
+        "the kernel must select the same expert set as torch.topk on CUDA"
+
+
+def test_topk_set_equals_torch_topk_cuda_on_real_logits():
+    """Benchmark-shaped routing (4096 tokens, Zipf router bias): from the kernel's
+    own bf16 logits the selected expert set equals torch.topk(softmax) on CUDA row
+    for row; from x, against the library GEMM's logits (cuBLAS order instead of
+    the fixed order), every row whose set differs has a logit that differs."""
+    from sparse_b200 import ops
+    shape = synth.QWEN_MOE
+    w = block_weights("QWEN_MOE", 1.2)
+    x = synth.make_hidden(4096, shape.hidden, seed=1).to(torch.bfloat16).to(dev())
+    wg = w.router.to(torch.bfloat16).to(dev())
+    bias = w.router_bias.to(torch.bfloat16).to(dev())
+    idx, wts, logits, _ = ops.router_topk(x, wg, shape.top_k, bias=bias)
+    ours = idx.long().sort(dim=1).values
+    _, ti = torch.topk(torch.softmax(logits, dim=-1, dtype=torch.float32), shape.top_k, dim=-1)
+    assert torch.equal(ti.sort(dim=1).values, ours), "same logits -> same set as torch.topk on CUDA"
+    ordered = float((ti == idx.long()).all(dim=1).float().mean())
+    assert ordered > 0.9                      # order inside a row differs only between tied experts
+    # the reference's gate call on this device (library GEMM, its own summation order)
+    lib_logits = torch.nn.functional.linear(x, wg, bias)
+    _, tl = torch.topk(torch.softmax(lib_logits, dim=-1, dtype=torch.float32), shape.top_k, dim=-1)
+    set_differs = (tl.sort(dim=1).values != ours).any(dim=1)
+    flipped = (lib_logits != logits).any(dim=1)
+    assert int((set_differs & ~flipped).sum()) == 0
+    assert float(set_differs.float().mean()) < 0.02
+    # The library GEMM on this device sums in its own order and, with torch's
+    # default reduced-precision bf16 reductions, rounds partial sums: about a
+    # quarter of its logits sit one bf16 step away from the fixed-order fp32 sum
+    # (on the CPU, where the reference's goldens come from, fewer than 0.5 % do).
+    # The kernel stays within two steps of it everywhere.
+    assert int(_bf16_ulp_diff(lib_logits, logits).max()) <= 2
 
 
 # ----------------------------------------------------------------- permute ----
@@ -447,7 +490,10 @@ def test_layer_against_reference_golden(name):
     g = load_golden(name)
     shape, w, x, out, idx, wts, logits, _ = _run_layer(g["shape"], g["tokens"], g["zipf_s"], g["input_seed"])
     same_route = (idx == g["topi"]).all(dim=1)
-    assert float(same_route.float().mean()) > 0.85
+    # measured share of rows routed exactly as the reference's CPU run routed them
+    floor = {"qwen_bf16_zipf_t1": 1.0, "qwen_bf16_zipf_t64": 0.984, "qwen_bf16_zipf_t256": 0.980,
+             "qwen_bf16_t512": 0.962, "qwen_bf16_zipf_t4096": 0.974, "tiny_bf16_t130": 1.0}[name]
+    assert float(same_route.float().mean()) >= floor
     rows = g["rows"]
     keep = same_route[rows]
     got, want = out[rows][keep], g["out_rows"][keep]
