@@ -122,6 +122,13 @@ def main():
         # One step in which the ranks take different branches: rank 0 sends a
         # decode-sized batch, the others a prefill-sized one, so the decode-sized
         # rank receives expert groups far above 16 rows.  Eagerly and replayed.
+        # A row may be computed by the streaming kernels on one rank and by the
+        # tile kernel on another (fp32 summation order differs), so rows are
+        # compared within the layer tolerance, not bit for bit.
+        def close(a, b):
+            a, b = a.double(), b.double()
+            return float((a - b).norm() / b.norm()) < 5e-3 and float((a - b).abs().max()) < 2e-2
+
         t_mix = 8 if rank == 0 else 97
         ref_mix = LayerRunner(LayerWeights.from_block_weights(w, dev), shape.top_k, 128)
         xm = [synth.make_hidden(t_mix, shape.hidden, seed=1300 + 10 * it + rank).to(torch.bfloat16).to(dev)
@@ -131,14 +138,14 @@ def main():
             out = blk.forward_device(xm[it]).clone()
             torch.cuda.synchronize()
             blk.check_status()
-            assert torch.equal(out, want_mix[it]), "mixed-branch EP rows differ on rank %d" % rank
+            assert close(out, want_mix[it]), "mixed-branch EP rows differ on rank %d" % rank
         dist.barrier()
         blk.use_graphs = True
         for it in range(4):          # first use of each buffer records, later ones replay
             out = blk.forward_device(xm[it % 2]).clone()
             torch.cuda.synchronize()
             blk.check_status()
-            assert torch.equal(out, want_mix[it % 2]), "graph-replayed mixed-branch rows differ on rank %d" % rank
+            assert close(out, want_mix[it % 2]), "graph-replayed mixed-branch rows differ on rank %d" % rank
         # the prefill-sized step through the block's own graph cache
         xg = [synth.make_hidden(tokens, shape.hidden, seed=1500 + 10 * it + rank).to(torch.bfloat16).to(dev)
               for it in range(2)]

@@ -164,8 +164,11 @@ def test_topk_set_equals_torch_topk_cuda_on_real_logits():
     # default reduced-precision bf16 reductions, rounds partial sums: about a
     # quarter of its logits sit one bf16 step away from the fixed-order fp32 sum
     # (on the CPU, where the reference's goldens come from, fewer than 0.5 % do).
-    # The kernel stays within two steps of it everywhere.
-    assert int(_bf16_ulp_diff(lib_logits, logits).max()) <= 2
+    # The kernel stays within two steps of it everywhere (a step taken at
+    # magnitude 1 for the logits near zero, whose partial sums are that large).
+    a, b = lib_logits.float(), logits.float()
+    step = torch.maximum(torch.maximum(a.abs(), b.abs()), torch.ones_like(a)) * 2.0 ** -7
+    assert bool(((a - b).abs() <= 2 * step).all())
 
 
 # ----------------------------------------------------------------- permute ----
