@@ -551,6 +551,159 @@ def offload_methods(args):
                   "%d warm-up steps" % (steps - warm, warm)}, "methods": out})
 
 
+def cache_stress(args):
+    """Opt-in (`--cache-stress`, launched like the bench at N > 1): decode steps of
+    one token per GPU through a stack of Qwen-shaped MoE layers (MoE layers only,
+    residual stream between them) with round-robin expert ownership, where every
+    GPU also keeps a quarter of the experts it does NOT own in LRU cache slots
+    filled from the owners' GPUs over NVLink.  Modes:
+
+      owner   no caching: every non-owned expert's rows go to its owner (plain EP decode)
+      rr      reactive LRU: a selected expert that is not cached is copied now,
+              on the compute stream, then run locally (the copy time is exposed)
+      rs      rr + a next-layer prefetch plan issued one layer ahead on a side
+              stream; the predictor emits 8 guesses per layer of which each true
+              expert survives with probability 0.7 (seeded)
+      sparse  rs + readiness scheduling: what is not here (or still in flight)
+              when the layer starts goes to its owner instead of being waited for
+
+    Reports decode tokens/s (host wall clock: the path synchronises once per
+    layer to read the routing back), exposed load time, hit rates and bytes."""
+    import random
+    import torch.distributed as dist
+    from sparse_b200 import synth
+    from sparse_b200.context import Metrics
+    from sparse_b200.peer_cache import LocalCacheEpLayer, build_rank_layer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--cache-stress needs at least 2 ranks (torch.distributed.run, one rank per GPU)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group(backend="nccl", device_id=dev)
+    shape = synth.QWEN_MOE
+    layers_n, steps, warm = args.stress_layers, args.stress_steps, args.stress_warmup
+    e_n, k = shape.num_experts, shape.top_k
+    owner_of = [e % world for e in range(e_n)]
+    non_owned = e_n - sum(1 for e in range(e_n) if e % world == rank)
+    cache_slots = max(1, int(0.25 * (e_n - e_n / world)))
+    w = synth.make_weights(shape, weight_seed=0, zipf_s=0.0)      # no router skew: the cache sees the whole expert set
+    built = []
+    for l in range(layers_n):
+        lw, slab, owned, slot_at_owner = build_rank_layer(w, dev, rank, world, owner_of, cache_slots)
+        slab.exchange(dist.group.WORLD)
+        built.append((lw, slab, owned, slot_at_owner))
+    torch.cuda.synchronize()
+    dist.barrier()
+    x0 = [synth.make_hidden(1, shape.hidden, seed=40000 + 131 * s_ + rank).to(torch.bfloat16).to(dev)
+          for s_ in range(warm + steps)]
+
+    def make_layers(miss, late, metrics):
+        return [LocalCacheEpLayer(b[0], b[1], b[2], b[3], owner_of, k, 16, rank, world, dist.group.WORLD,
+                                  cache_slots, miss=miss, late=late, metrics=metrics, layer_idx=l)
+                for l, b in enumerate(built)]
+
+    def predictor(truth_row, step, layer):
+        rng = random.Random(1000003 * step + 1009 * layer + rank)
+        guess = [e for e in truth_row if rng.random() < 0.7]
+        others = [e for e in range(e_n) if e not in truth_row]
+        rng.shuffle(others)
+        guess += others[:8 - len(guess)]
+        return {e: 1.0 - 0.05 * i for i, e in enumerate(guess)}
+
+    def run(mode, truth=None):
+        miss, late, prefetch = {"owner": ("owner", "owner", False), "rr": ("load", "wait", False),
+                                "rs": ("load", "wait", True), "sparse": ("owner", "owner", True)}[mode]
+        metrics = Metrics()
+        lay = make_layers(miss, late, metrics)
+        if mode == "owner":
+            for ly in lay:
+                ly.store.cache.capacity = 0          # nothing is ever admitted: plain owner routing
+        record = [] if truth is None else None
+        outs = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        t_start = None
+        snap = None
+        for s_ in range(warm + steps):
+            if s_ == warm:
+                torch.cuda.synchronize()
+                dist.barrier()
+                snap = (metrics.load_exposed_ms, metrics.expert_weight_peer_bytes, metrics.cache_hit_count,
+                        metrics.cache_miss_count, metrics.local_cached_item_count, metrics.owner_fallback_item_count,
+                        metrics.prefetch_admitted_count, metrics.prefetch_complete_before_use_count,
+                        metrics.prefetch_late_count)
+                t_start = time.perf_counter()
+            x = x0[s_]
+            row = []
+            if prefetch:
+                lay[0].begin_step()
+                lay[0].prefetch(predictor(truth[s_][0], s_, 0), budget=args.stress_budget)
+            for l in range(layers_n):
+                if prefetch and l + 1 < layers_n:
+                    lay[l + 1].begin_step()
+                    lay[l + 1].prefetch(predictor(truth[s_][l + 1], s_, l + 1), budget=args.stress_budget)
+                y = lay[l].forward(x)
+                if record is not None:
+                    row.append(lay[l]._idx_host[0].tolist())     # already on the host
+                x = x + y
+            if record is not None:
+                record.append(row)
+            outs = x
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t_start
+        for ly in lay:
+            ly.check_status()
+            metrics.finalize_events()
+        v = torch.tensor([wall], dtype=torch.float64, device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        wall = float(v.item())
+        now = (metrics.load_exposed_ms, metrics.expert_weight_peer_bytes, metrics.cache_hit_count,
+               metrics.cache_miss_count, metrics.local_cached_item_count, metrics.owner_fallback_item_count,
+               metrics.prefetch_admitted_count, metrics.prefetch_complete_before_use_count,
+               metrics.prefetch_late_count)
+        d = [a - b for a, b in zip(now, snap)]
+        tot = torch.tensor(d, dtype=torch.float64, device=dev)
+        dist.all_reduce(tot)                                   # summed over ranks
+        d = tot.tolist()
+        res = {"decode_tokens_per_s": world * steps / wall, "ms_per_step": wall / steps * 1e3,
+               "us_per_layer": wall / steps / layers_n * 1e6,
+               "exposed_load_ms_per_step_per_gpu": d[0] / steps / world,
+               "peer_weight_mb_per_step_per_gpu": d[1] / steps / world / 1e6,
+               "cache_hits": int(d[2]), "cache_misses": int(d[3]),
+               "items_run_locally_from_cache": int(d[4]), "items_sent_to_owner_for_lack_of_weights": int(d[5]),
+               "prefetch_admitted": int(d[6]), "prefetch_ready_before_use": int(d[7]), "prefetch_late": int(d[8])}
+        del lay
+        return res, record, outs
+
+    res_owner, truth, out_ref = run("owner")
+    results = {"owner": res_owner}
+    same = 1
+    for mode in ("rr", "rs", "sparse"):
+        results[mode], _, out_m = run(mode, truth)
+        if not torch.equal(out_m, out_ref):
+            same = 0
+    flag = torch.tensor([same], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        emit({"metric": "cache_stress_decode_tokens_per_s", "n_gpus": world, "unit": "tokens/s",
+              "config": {"workload": "qwen1.5-moe-a2.7b-shaped MoE layers only (no router skew), %d layers, 1 token per GPU per decode "
+                                     "step, %d steps after %d warm-up steps, round-robin ownership at EP=%d, %d LRU "
+                                     "slots per layer per GPU for non-owned experts (25%% of %d), weights copied "
+                                     "from the owner GPU over NVLink" % (layers_n, steps, warm, world, cache_slots,
+                                                                         non_owned),
+                         "predictor": "synthetic: 8 guesses per layer, each true expert kept with probability 0.7 "
+                                      "(seeded), prefetch budget %d per layer" % args.stress_budget,
+                         "not_included": "attention and the 32768-token prefill of the full-model configuration"},
+              "modes": results,
+              "final_hidden_state_identical_in_all_modes": bool(int(flag.item())),
+              "timing": "host wall clock, max over ranks (one host synchronisation per layer reads the routing back)"})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_ours(args):
     from sparse_b200 import synth
     from sparse_b200.block import B200MoeBlock
@@ -946,6 +1099,13 @@ def main():
     ap.add_argument("--placement", default="balanced",
                     help="expert placement at N>1: balanced (load-balanced replicated, default), rr "
                          "(round-robin) or perm:<seed> (seeded random permutation, one owner per expert)")
+    ap.add_argument("--cache-stress", action="store_true",
+                    help="instead of the layer bench: decode steps at N>1 with non-owned experts cached locally "
+                         "(owner / rr / rs / sparse)")
+    ap.add_argument("--stress-layers", type=int, default=24)
+    ap.add_argument("--stress-steps", type=int, default=512)
+    ap.add_argument("--stress-warmup", type=int, default=32)
+    ap.add_argument("--stress-budget", type=int, default=4)
     ap.add_argument("--offload-methods", action="store_true",
                     help="instead of the layer bench: decode steps with host-resident experts under rr/epipe/rs/rs-epipe")
     args = ap.parse_args()
@@ -954,6 +1114,9 @@ def main():
         ap.error("--placement must be balanced, rr or perm:<seed>")
     if args.offload_methods:
         offload_methods(args)
+        return
+    if args.cache_stress:
+        cache_stress(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)

@@ -70,8 +70,8 @@ int32_t sb_init(int32_t device);
  * are bit-identical under every setting, only the time changes.
  *   "sched"          0 = walk the tile table in order with a fixed stride,
  *                    1 = rank the row chunks by size and deal them out
- *                        boustrophedon (default), 2 = as 1 with odd CTA pairs
- *                        walking their list backwards
+ *                        boustrophedon, 2 = as 1 with odd CTA pairs walking
+ *                        their list backwards (default)
  *   "dense_group"    row chunks per raster block of a dense (shared-expert)
  *                    pass, 1..64 (default 1)
  *   "router_overlap" 1 = sb_moe_layer_forward runs the router beside the shared
@@ -219,13 +219,24 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
                           int32_t R_cap, int32_t H, int32_t I, int32_t S,
                           void *hbuf, void *out, int32_t *status, void *stream);
 
+/* The routed part of sb_decode_experts with every result row stored at its own
+ * address (`row_dst` uint64 [rows of the tile table], 0 = drop) instead of into
+ * a dense output buffer: rows of the local expert sort go straight to the rows
+ * of a return buffer that a later sb_combine reads (see
+ * sb_ep_exchange_dispatch_local).  Groups of any size (swept 16 rows at a time). */
+int32_t sb_decode_experts_to(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
+                             const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
+                             const void *w2, const void *row_scale, int32_t H, int32_t I, int32_t n_slots,
+                             void *hbuf, const uint64_t *row_dst, int32_t *status, void *stream);
+
 /* sb_grouped_swiglu restricted to one of its two passes: `passes` 1 = gate/up +
  * SwiGLU into `hbuf`, 2 = down projection from `hbuf` into `out`, 3 = both.
  * Lets a caller put other work (a transfer on another stream) between the
  * passes of the shared expert.  `stages` is the depth of the kernel's
- * shared-memory pipeline, 2..6 (0 = 6): with 5 an SM keeps enough shared memory
- * and registers free for one CTA of sb_router_topk launched on another stream,
- * which is how the router is hidden behind the shared expert's gate/up pass. */
+ * shared-memory pipeline, 2..6 (0 = the default 5): with at most 5 an SM keeps
+ * enough shared memory and registers free for one CTA of sb_router_topk launched
+ * on another stream, which is how the router is hidden behind the shared
+ * expert's gate/up pass. */
 int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,
                                  const void *w13, const void *w2, const int32_t *slot_of_expert,
                                  const void *row_scale, int32_t R_cap, int32_t H, int32_t I, int32_t S,
@@ -412,6 +423,28 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
                                 void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
                                 void *const *peer_meta, void *const *peer_ret, int32_t ret_rows,
                                 uint64_t *row_dst, int32_t *status, void *stream);
+
+/* sb_ep_exchange_dispatch for a rank that executes some experts it does not own
+ * out of its own cache slots ("run locally if the weights are here, else at the
+ * owner": the idea of the reference's _light_destinations,
+ * utils/eval_core.py:6396-6411).  `local_map` (int32 [E], NULL = none): >= 0
+ * for an expert whose items stay here.  Their counts are published as 0, their
+ * rows are not sent, `item_rank[i]` = this rank and `item_row[i]` = i, and
+ * `local_dst[s]` (uint64 [n_items]) receives, for every row s of the local
+ * expert sort, the address of row `item_of_slot[s]` of this rank's own return
+ * buffer: what sb_decode_experts takes as `row_dst` to put locally computed
+ * rows where the combine expects them.  Needs `peer_meta` (return addresses). */
+int32_t sb_ep_exchange_dispatch_local(const int32_t *local_offsets, void *const *peer_counts,
+                                      void *const *peer_flags, uint32_t *epoch_counter, const int32_t *owner,
+                                      int32_t E, int32_t rank, int32_t ep, int32_t recv_cap, int32_t *dst_base,
+                                      int32_t *recv_offsets, int32_t *tile_table, const void *x,
+                                      const int32_t *item_expert, const void *item_scale,
+                                      const int32_t *slot_of_item, int32_t n_items, int32_t items_per_row,
+                                      int32_t H, void *const *peer_rows, void *const *peer_scale,
+                                      int32_t *item_rank, int32_t *item_row, void *const *peer_meta,
+                                      void *const *peer_ret, int32_t ret_rows, uint64_t *row_dst,
+                                      const int32_t *local_map, const int32_t *item_of_slot, uint64_t *local_dst,
+                                      int32_t *status, void *stream);
 
 /* Copy every item's activation row and route weight into its row of the
  * owner's receive buffers (`peer_rows[d]` [recv_cap,H] bf16, `peer_scale[d]`

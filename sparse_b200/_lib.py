@@ -59,6 +59,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_decode_experts": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32,
                                 vp, vp, vp, vp]),
+    "sb_decode_experts_to": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]),
     "sb_grouped_swiglu_mixed": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp,
                                       i32, i32, vp, vp, vp, vp, vp]),
     "sb_route_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
@@ -77,6 +78,9 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_ep_exchange_dispatch": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp, vp,
                                       vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp,
                                       C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),
+    "sb_ep_exchange_dispatch_local": (i32, [vp, C.POINTER(vp), C.POINTER(vp), vp, vp, i32, i32, i32, i32, vp, vp,
+                                            vp, vp, vp, vp, vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), vp, vp,
+                                            C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp, vp, vp, vp]),
     "sb_ep_plan": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_dispatch": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                              C.POINTER(vp), C.POINTER(vp), vp, vp, i32, C.POINTER(vp), vp]),

@@ -64,6 +64,12 @@ class Metrics:
     expert_weight_h2d_bytes: int = 0
     expert_weight_h2d_demand_bytes: int = 0
     expert_weight_h2d_prefetch_bytes: int = 0
+    expert_weight_peer_bytes: int = 0              # weights copied from an owner GPU's slab over NVLink
+    expert_weight_peer_demand_bytes: int = 0
+    expert_weight_peer_prefetch_bytes: int = 0
+    local_cached_item_count: int = 0               # items of non-owned experts executed out of a local cache slot
+    owner_fallback_item_count: int = 0             # items sent to the owner because the weights were not (yet) here
+    load_exposed_ms: float = 0.0                   # compute-stream time spent waiting for weight copies
     cache_hit_count: int = 0
     cache_miss_count: int = 0
     prefetch_issued_count: int = 0
@@ -105,6 +111,8 @@ class Metrics:
                 keep.append((kind, phase, start, end))
                 continue
             ms = float(start.elapsed_time(end))
+            if kind == "load_exposed":
+                self.load_exposed_ms += ms
             if kind == "demand_h2d":
                 self.demand_h2d_exposed_ms += ms
                 if phase == "prefill":

@@ -53,12 +53,16 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 }
 
 // counts_all on every rank: [ep][E]; this rank fills row `rank` everywhere.
+// Items of an expert that this rank executes itself out of a cache slot
+// (`local_map[e]` >= 0) take no part in the exchange: their count is published as 0.
 __device__ __forceinline__ void publish_body(const int32_t *__restrict__ local_offsets, int E, int rank, int ep,
-                                             const PeerPtrs &counts_all) {
+                                             const PeerPtrs &counts_all,
+                                             const int32_t *__restrict__ local_map = nullptr) {
   for (int i = threadIdx.x; i < E * ep; i += blockDim.x) {
     int p = i / E, e = i - p * E;
     int32_t *dst = static_cast<int32_t *>(counts_all.p[p]) + (size_t)rank * E + e;
-    *dst = local_offsets[e + 1] - local_offsets[e];
+    const bool kept = local_map != nullptr && local_map[e] >= 0;
+    *dst = kept ? 0 : local_offsets[e + 1] - local_offsets[e];
   }
 }
 
@@ -191,13 +195,19 @@ __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const
                                               const PeerPtrs &recv_rows, const PeerPtrs &recv_scale,
                                               int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
                                               int first_warp, int warps_total, int rank = 0,
-                                              const PeerPtrs *recv_meta = nullptr) {
+                                              const PeerPtrs *recv_meta = nullptr,
+                                              const int32_t *__restrict__ local_map = nullptr) {
   const int lane = threadIdx.x & 31;
   for (int i = first_warp; i < n_items; i += warps_total) {
     const int e = item_expert[i];
     const int slot = slot_of_item[i];
     if (e < 0 || slot < 0) {
       if (lane == 0) { item_rank[i] = -1; item_row[i] = -1; }
+      continue;
+    }
+    if (local_map != nullptr && local_map[e] >= 0) {
+      // executed here out of a cache slot: the result lands in row i of this rank's own return buffer
+      if (lane == 0) { item_rank[i] = rank; item_row[i] = i; }
       continue;
     }
     const int d = owner[e];
@@ -270,9 +280,20 @@ ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs 
                             int vec_per_row, int recv_cap, PeerPtrs recv_rows, PeerPtrs recv_scale,
                             int32_t *__restrict__ item_rank, int32_t *__restrict__ item_row,
                             int32_t *__restrict__ status, int with_meta, PeerPtrs recv_meta, PeerPtrs ret,
-                            int ret_rows, unsigned long long *__restrict__ row_dst) {
+                            int ret_rows, unsigned long long *__restrict__ row_dst,
+                            const int32_t *__restrict__ local_map, const int32_t *__restrict__ item_of_slot,
+                            unsigned long long *__restrict__ local_dst) {
   extern __shared__ int plan_smem[];
-  publish_body(local_offsets, E, rank, ep, counts_all);
+  publish_body(local_offsets, E, rank, ep, counts_all, local_map);
+  if (local_map != nullptr && local_dst != nullptr) {
+    // return address of every locally sorted row (row s of the local sort is item item_of_slot[s])
+    char *mine = static_cast<char *>(ret.p[rank]);
+    for (int s = threadIdx.x; s < n_items; s += blockDim.x) {
+      const int it = item_of_slot[s];
+      local_dst[s] = (it >= 0 && it < ret_rows)
+                         ? reinterpret_cast<unsigned long long>(mine + (size_t)it * vec_per_row * 16) : 0ull;
+    }
+  }
   __threadfence_system();
   uint32_t epoch = next_epoch(epoch_counter);
   barrier_body(flags, rank, ep, epoch, status);
@@ -282,7 +303,7 @@ ep_exchange_dispatch_kernel(const int32_t *__restrict__ local_offsets, PeerPtrs 
   __syncthreads();                      // dst_base (global, written by this CTA) is visible to all its threads
   dispatch_body(x, item_expert, item_scale, slot_of_item, local_offsets, dst_base, owner + (size_t)rank * E,
                 n_items, items_per_row, vec_per_row, recv_cap, recv_rows, recv_scale, item_rank, item_row,
-                threadIdx.x >> 5, blockDim.x >> 5, rank, with_meta ? &recv_meta : nullptr);
+                threadIdx.x >> 5, blockDim.x >> 5, rank, with_meta ? &recv_meta : nullptr, local_map);
   __threadfence_system();
   epoch = next_epoch(epoch_counter);
   barrier_body(flags, rank, ep, epoch, status);
@@ -480,6 +501,27 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
                                 void *const *peer_scale, int32_t *item_rank, int32_t *item_row,
                                 void *const *peer_meta, void *const *peer_ret, int32_t ret_rows,
                                 uint64_t *row_dst, int32_t *status, void *stream) {
+  return sb_ep_exchange_dispatch_local(local_offsets, peer_counts, peer_flags, epoch_counter, owner, E, rank, ep,
+                                       recv_cap, dst_base, recv_offsets, tile_table, x, item_expert, item_scale,
+                                       slot_of_item, n_items, items_per_row, H, peer_rows, peer_scale, item_rank,
+                                       item_row, peer_meta, peer_ret, ret_rows, row_dst, nullptr, nullptr, nullptr,
+                                       status, stream);
+}
+
+int32_t sb_ep_exchange_dispatch_local(const int32_t *local_offsets, void *const *peer_counts,
+                                      void *const *peer_flags, uint32_t *epoch_counter, const int32_t *owner,
+                                      int32_t E, int32_t rank, int32_t ep, int32_t recv_cap, int32_t *dst_base,
+                                      int32_t *recv_offsets, int32_t *tile_table, const void *x,
+                                      const int32_t *item_expert, const void *item_scale,
+                                      const int32_t *slot_of_item, int32_t n_items, int32_t items_per_row,
+                                      int32_t H, void *const *peer_rows, void *const *peer_scale,
+                                      int32_t *item_rank, int32_t *item_row, void *const *peer_meta,
+                                      void *const *peer_ret, int32_t ret_rows, uint64_t *row_dst,
+                                      const int32_t *local_map, const int32_t *item_of_slot, uint64_t *local_dst,
+                                      int32_t *status, void *stream) {
+  if (local_map != nullptr && (!peer_meta || !item_of_slot || !local_dst))
+    return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch_local: local_map needs return addresses, item_of_slot "
+                                  "and local_dst");
   if (!local_offsets || !epoch_counter || !owner || !dst_base || !recv_offsets || !tile_table || E < 1 ||
       E > kMaxExperts || rank < 0 || rank >= ep || ep > kMaxRanks || recv_cap < 0)
     return fail(SB_E_INVALID_ARG, "sb_ep_exchange_dispatch: bad arguments (E=%d rank=%d ep=%d)", E, rank, ep);
@@ -511,7 +553,8 @@ int32_t sb_ep_exchange_dispatch(const int32_t *local_offsets, void *const *peer_
       local_offsets, pc, pf, epoch_counter, owner, E, rank, ep, tile_cap, sb_tile_rows(), dst_base, recv_offsets,
       tile_table, static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),
       slot_of_item, n_items, items_per_row, H / 8, recv_cap, pr, ps, item_rank, item_row, status, with_meta, pm,
-      pt, ret_rows, reinterpret_cast<unsigned long long *>(row_dst));
+      pt, ret_rows, reinterpret_cast<unsigned long long *>(row_dst), local_map, item_of_slot,
+      reinterpret_cast<unsigned long long *>(local_dst));
   SB_LAUNCH_CHECK();
   return SB_OK;
 }

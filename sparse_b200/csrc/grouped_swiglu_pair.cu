@@ -54,7 +54,8 @@ constexpr int kTileW = 256;          // weight rows per CTA pair (MMA M)
 constexpr int kRowsPerCta = 128;
 constexpr int kMaxN = 256;           // tokens per tile (MMA N), multiple of 16
 constexpr int kBlockK = 64;
-constexpr int kStages = 6;
+constexpr int kStages = 6;           // most the shared memory holds
+constexpr int kDefaultStages = 5;    // measured on B200: a sixth stage gains nothing (the operand fetch is bandwidth-, not latency-bound)
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 320;         // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpiWarps = 8;
@@ -536,7 +537,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 }
 
 // Tuning knobs behind sb_set_tuning (process-wide, read at launch time).
-std::atomic<int> g_sched_mode{1};      // 0 table order / fixed stride, 1 ranked boustrophedon, 2 odd pairs backwards
+std::atomic<int> g_sched_mode{2};      // 0 table order / fixed stride, 1 ranked boustrophedon, 2 odd pairs backwards
 std::atomic<int> g_dense_group{1};     // dense passes: row chunks per raster block (1 = chunk-major walk)
 int sched_mode() { return g_sched_mode.load(std::memory_order_relaxed); }
 
@@ -694,7 +695,7 @@ int32_t set_gemm_tuning(const char *key, int value) {
 // row, 0 = drop) the down pass writes each result row to that address instead
 // of `out`.  `passes`: 1 = gate/up + SwiGLU only, 2 = down only (hbuf already
 // holds the intermediate rows), 3 = both.  `stages` in [2, 6] is the depth of
-// the shared-memory pipeline (0 = 6); 5 leaves room on the SM for a router CTA.
+// the shared-memory pipeline (0 = 5, which leaves room on the SM for a router CTA).
 int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, int dense_rows, const void *w13,
                                    const void *w2, const int32_t *slot_of_expert, const void *row_scale,
                                    int R_cap, int H, int I, int S, void *hbuf, void *out, int32_t *status,
@@ -709,7 +710,7 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (!rows || !w13 || !w2 || !hbuf || (!out && !row_dst)) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
   if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || (out && !aligned(out, 16)))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
-  if (stages == 0) stages = kStages;
+  if (stages == 0) stages = kDefaultStages;
   if (stages < 2 || stages > kStages) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: stages=%d outside [2,%d]", stages, kStages);
   int32_t rc = prepare_device();
   if (rc != SB_OK) return rc;

@@ -40,13 +40,21 @@ class LayerWeights:
     """Weights of one MoE layer on one GPU."""
 
     def __init__(self, hidden: int, inter: int, num_experts: int, n_slots: int,
-                 shared_inter: int, device: torch.device):
+                 shared_inter: int, device: torch.device, w13: Optional[torch.Tensor] = None,
+                 w2: Optional[torch.Tensor] = None):
+        """`w13` / `w2`: slabs the caller already owns (e.g. memory that peer GPUs
+        have mapped, `peer_cache.PeerSlab`); allocated here when omitted."""
         self.hidden, self.inter, self.num_experts = hidden, inter, num_experts
         self.n_slots, self.shared_inter = n_slots, shared_inter
         self.device = device
         bf = torch.bfloat16
-        self.w13 = torch.empty((n_slots, 2 * inter, hidden), dtype=bf, device=device)
-        self.w2 = torch.empty((n_slots, hidden, inter), dtype=bf, device=device)
+        if (w13 is None) != (w2 is None):
+            raise ValueError("w13 and w2 slabs go together")
+        if w13 is not None and (tuple(w13.shape) != (n_slots, 2 * inter, hidden) or
+                                tuple(w2.shape) != (n_slots, hidden, inter) or w13.dtype != bf or w2.dtype != bf):
+            raise ValueError("external slabs must be bf16 [S,2I,H] and [S,H,I]")
+        self.w13 = w13 if w13 is not None else torch.empty((n_slots, 2 * inter, hidden), dtype=bf, device=device)
+        self.w2 = w2 if w2 is not None else torch.empty((n_slots, hidden, inter), dtype=bf, device=device)
         self.slot_of_expert = torch.full((num_experts,), -1, dtype=torch.int32, device=device)
         self.router_w: Optional[torch.Tensor] = None
         self.router_bias: Optional[torch.Tensor] = None      # fp32 [E], bf16-rounded values

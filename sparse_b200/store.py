@@ -60,12 +60,15 @@ class ExpertStore:
 
     def __init__(self, weights: LayerWeights, host: HostExperts, cache_capacity: int,
                  staging_slots: int = 1, resident: Sequence[int] = (), cfg: Optional[BlockConfig] = None,
-                 metrics: Optional[Metrics] = None, layer_idx: int = 0):
+                 metrics: Optional[Metrics] = None, layer_idx: int = 0, peers=None):
+        """`peers`: a `peer_cache.PeerExperts` naming, for experts without a host
+        copy here, the owner GPU's slab rows to copy from over NVLink."""
         need = len(resident) + cache_capacity + staging_slots
         if weights.n_slots < need:
             raise RuntimeError("slab has %d slots, need %d (resident %d + cache %d + staging %d)" % (
                 weights.n_slots, need, len(resident), cache_capacity, staging_slots))
         self.w, self.host, self.cfg = weights, host, cfg or BlockConfig()
+        self.peers = peers
         self.metrics, self.layer_idx = metrics, layer_idx
         self.device = weights.device
         self.num_experts = weights.num_experts
@@ -110,7 +113,17 @@ class ExpertStore:
     # -- copies -------------------------------------------------------------------
     def _copy_into(self, slot: int, expert: int, stream: torch.cuda.Stream, prefetch: bool) -> None:
         if expert not in self.host:
-            raise RuntimeError("expert %d has no host copy on this rank" % expert)
+            if self.peers is None or expert not in self.peers:
+                raise RuntimeError("expert %d has neither a host copy nor a peer copy on this rank" % expert)
+            # owner GPU's slab rows -> this slot, two plain async copies over NVLink
+            n = self.peers.copy_into(self.w, slot, expert, stream)
+            if self.metrics is not None:
+                self.metrics.expert_weight_peer_bytes += n
+                if prefetch:
+                    self.metrics.expert_weight_peer_prefetch_bytes += n
+                else:
+                    self.metrics.expert_weight_peer_demand_bytes += n
+            return
         ops.slot_copy_async(self.w.w13[slot], self.host.w13[expert], stream, _lib.SB_COPY_HOST_TO_DEVICE)
         ops.slot_copy_async(self.w.w2[slot], self.host.w2[expert], stream, _lib.SB_COPY_HOST_TO_DEVICE)
         if self.metrics is not None:

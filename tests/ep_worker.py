@@ -69,6 +69,62 @@ def offloaded_case(rank, world, dev):
         dist.barrier()
 
 
+def local_cache_case(rank, world, dev):
+    """Non-owned experts in local cache slots, filled from the owner GPU over
+    NVLink: whatever runs locally and whatever goes to the owner, a decode-sized
+    step gives the rows of the all-resident EP layer bit for bit, under every
+    miss / late policy, with and without a prefetch plan."""
+    from sparse_b200.context import Metrics
+    from sparse_b200.peer_cache import LocalCacheEpLayer, build_rank_layer
+    for shape_name, cache_slots in (("TINY", 2), ("QWEN_MOE", 6)):
+        shape = getattr(synth, shape_name)
+        w = synth.make_weights(shape, weight_seed=0, zipf_s=1.2)
+        owner_of = [e % world for e in range(shape.num_experts)]
+        ref = B200MoeBlock.from_block_weights(w, dev, ep_rank=rank, ep_size=world, max_tokens=16,
+                                              process_group=dist.group.WORLD)
+        lw, slab, owned, slot_at_owner = build_rank_layer(w, dev, rank, world, owner_of, cache_slots)
+        slab.exchange(dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier()                       # every owner's slab is loaded before anyone copies from it
+        xs = [synth.make_hidden(4 if rank == 0 else 3, shape.hidden, seed=2100 + 10 * it + rank)
+              .to(torch.bfloat16).to(dev) for it in range(6)]
+        wants, chosen = [], []
+        for x in xs:
+            wants.append(ref.forward_device(x).clone())
+            chosen.append(ref.topk(x.shape[0])[0].clone())
+        torch.cuda.synchronize()
+        ref.check_status()
+        dist.barrier()
+        total_local = 0
+        for miss, late, prefetch in (("load", "wait", False), ("owner", "wait", False), ("load", "wait", True),
+                                     ("owner", "owner", True)):
+            metrics = Metrics()
+            lay = LocalCacheEpLayer(lw, slab, owned, slot_at_owner, owner_of, shape.top_k, 16, rank, world,
+                                    dist.group.WORLD, cache_slots, miss=miss, late=late, metrics=metrics)
+            for it, x in enumerate(xs):
+                lay.begin_step()
+                if prefetch:
+                    # a predictor that knows part of the truth: the experts of the step's first token
+                    guess = {int(e): 1.0 for e in chosen[it][0].tolist()}
+                    guess[(it * 3 + rank) % shape.num_experts] = 0.5
+                    lay.prefetch(guess, budget=2)
+                out = lay.forward(x).clone()
+                torch.cuda.synchronize()
+                lay.check_status()
+                assert torch.equal(out, wants[it]), "local-cache EP rows differ (rank %d, %s/%s, step %d)" % (
+                    rank, miss, late, it)
+                assert len(lay.store.cache.resident_ids()) <= cache_slots
+            if miss == "load":
+                assert metrics.local_cached_item_count > 0 and metrics.expert_weight_peer_bytes > 0
+            total_local += metrics.local_cached_item_count
+            dist.barrier()
+        assert total_local > 0
+        del lay, ref
+        torch.cuda.synchronize()
+        dist.barrier()
+        slab.close()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -158,6 +214,7 @@ def main():
         blk.use_graphs = False
         dist.barrier()
     offloaded_case(rank, world, dev)
+    local_cache_case(rank, world, dev)
     print("EP_WORKER_OK rank %d" % rank, flush=True)
     dist.barrier()
     dist.destroy_process_group()
