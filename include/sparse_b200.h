@@ -536,6 +536,39 @@ size_t sb_moe_layer_workspace_bytes(int32_t T, int32_t H, int32_t E, int32_t K,
  */
 int32_t sb_moe_layer_forward(const sb_moe_layer *layer, int32_t *status, void *stream);
 
+/*
+ * The small kernels of a decode step around the MoE layers (the reference runs
+ * these through the Transformers model classes it loads at
+ * utils/eval_core.py:17807-17829 and calls once per generated token from the
+ * loop at 18464-18607).  All tensors bf16, row-major.
+ *
+ * sb_add_rmsnorm   residual [T,H] += delta (+ delta2), rounded to bf16 after each
+ *                  add and written back (delta NULL: no add, no write-back);
+ *                  out = weight * bf16(h * rsqrt(mean(h^2) + eps)).  out NULL:
+ *                  only the residual update.
+ * sb_rope_append   rotary embedding (pairs (i, i + rope_dim/2) of the first
+ *                  rope_dim elements, angle pos * theta^(-2i/rope_dim), cos/sin
+ *                  rounded to bf16) on q [T,n_q,dk] in place and on k
+ *                  [T,n_kv,dk]; rotated k and v [T,n_kv,dv] are stored into the
+ *                  cache rows (seq_of_token[t], pos_of_token[t]) of cache_k
+ *                  [B,s_max,n_kv,dk] / cache_v [B,s_max,n_kv,dv].
+ * sb_attn_decode   one query per sequence, q [B,n_q,dk], against the first
+ *                  seq_lens[b] (device int32) cached positions; softmax in fp32;
+ *                  out [B,n_q,dv].  The keys are split `n_split` ways over CTAs
+ *                  and merged by a second kernel; ws needs
+ *                  sb_attn_decode_workspace_bytes.  Built for (dk,dv) =
+ *                  (128,128), (192,128), (64,64).
+ */
+int32_t sb_add_rmsnorm(void *residual, const void *delta, const void *delta2, const void *weight, float eps,
+                       int32_t T, int32_t H, void *out, void *stream);
+int32_t sb_rope_append(void *q, const void *k, const void *v, const int32_t *seq_of_token,
+                       const int32_t *pos_of_token, int32_t T, int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv,
+                       int32_t rope_dim, float theta, int32_t s_max, void *cache_k, void *cache_v, void *stream);
+size_t sb_attn_decode_workspace_bytes(int32_t B, int32_t n_q, int32_t dv, int32_t n_split);
+int32_t sb_attn_decode(const void *q, const void *cache_k, const void *cache_v, const int32_t *seq_lens, int32_t B,
+                       int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv, int32_t s_max, float scale,
+                       int32_t n_split, void *ws, size_t ws_bytes, void *out, void *stream);
+
 /* Number of kernels the last sb_moe_layer_forward of this thread launched. */
 int32_t sb_last_launch_count(void);
 

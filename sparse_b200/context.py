@@ -88,11 +88,18 @@ class Metrics:
     epipe_staged_expert_count: int = 0
     epipe_ready_group_count: int = 0
     epipe_fallback_count: int = 0
+    wall_prefill_ms: float = 0.0                   # greedy_decode_profiled's wall clocks (utils/eval_core.py:18511, 18590)
+    wall_decode_ms: float = 0.0
+    wall_ttft_ms: float = 0.0
+    warmup_time_ms: float = 0.0
+    peak_allocated_mb: float = 0.0
+    peak_reserved_mb: float = 0.0
     moe_router_ms: float = 0.0
     moe_expert_ms: float = 0.0
     moe_shared_ms: float = 0.0
     rs_counters: Dict[str, int] = field(default_factory=dict)
     pending_events: List[Any] = field(default_factory=list)   # (kind, phase, start_event, end_event)
+    decode_step_stats: Any = None                  # a RunningStats when per-step latencies are wanted
 
     def reset_for_repeat(self) -> None:
         fresh = Metrics()
@@ -122,6 +129,9 @@ class Metrics:
         self.pending_events = keep
 
     def summary(self) -> Dict[str, Any]:
-        out = {f.name: getattr(self, f.name) for f in fields(self) if f.name not in ("rs_counters", "pending_events")}
+        out = {f.name: getattr(self, f.name) for f in fields(self)
+               if f.name not in ("rs_counters", "pending_events", "decode_step_stats")}
+        if self.decode_step_stats is not None:
+            out.update(self.decode_step_stats.summary("decode_step_"))
         out.update({"rs_" + k if not k.startswith(("rs_", "prefetch_")) else k: v for k, v in self.rs_counters.items()})
         return out

@@ -224,7 +224,7 @@ class LocalCacheEpLayer(ExpertParallelLayer):
         want = {int(e): float(s) for e, s in scores.items() if int(e) not in self.owned_set}
         plan = build_prefetch_plan(want, st.cache, protect_ids=st.protect_ids(), budget=budget,
                                    min_score=min_score, replace_advantage=0.0, replace_margin=1.0,
-                                   allow_active_replace=False, is_local=lambda e: True, keep_bias=st.keep_bias)
+                                   allow_active_replace=True, is_local=lambda e: True, keep_bias=st.keep_bias)
         return st.admit_prefetch_plan(plan)
 
     def begin_step(self) -> None:
