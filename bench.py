@@ -709,6 +709,99 @@ def cache_stress(args):
     dist.destroy_process_group()
 
 
+def model_decode(args):
+    """Opt-in (`--model-decode qwen|deepseek`, launched like the bench at N > 1):
+    prefill + greedy decode through the whole shaped model (attention, norms,
+    MoE block in every layer, lm_head), random init, random token ids.
+      qwen      24 layers, 8 sequences x 2048 prompt ids (seed 2), 128 new tokens
+      deepseek  27 layers (layer 0 dense, MLA-shaped attention), 16 x 1024 (seed 3), 256 new tokens
+    The sequences are sharded over the ranks (data-parallel attention), the
+    experts by round-robin ownership.  Decode tokens/s as the reference counts
+    it: generated tokens minus the first one per sequence, over the decode wall
+    time (scripts/perf.py:2107-2120); every decode step is one CUDA-graph launch."""
+    from sparse_b200 import synth
+    from sparse_b200.context import Metrics
+    from sparse_b200.model import DEEPSEEK_MODEL, QWEN_MODEL, RunningStats, ShapedMoeModel, greedy_decode_profiled
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist = dist_
+        dist.init_process_group(backend="nccl", device_id=dev)
+    cfg, batch, prompt, new, seed = {"qwen": (QWEN_MODEL, 8, 2048, 128, 2),
+                                     "deepseek": (DEEPSEEK_MODEL, 16, 1024, 256, 3)}[args.model_decode]
+    if args.model_batch:
+        batch = args.model_batch
+    if args.model_prompt:
+        prompt = args.model_prompt
+    if args.model_new:
+        new = args.model_new
+    if batch % world != 0:
+        raise SystemExit("--model-decode: %d sequences do not divide over %d ranks" % (batch, world))
+    b_local = batch // world
+    peaks = _peaks()
+    model = ShapedMoeModel(cfg, dev, b_local, prompt + new + 1, seed=0, ep_rank=rank, ep_size=world,
+                           process_group=None if world == 1 else dist.group.WORLD, chunk_tokens=4096)
+    g = torch.Generator().manual_seed(seed)
+    ids_all = torch.randint(0, cfg.vocab, (batch, prompt), generator=g)
+    ids = ids_all[rank * b_local:(rank + 1) * b_local].to(dev)
+    metrics = Metrics()
+    metrics.decode_step_stats = RunningStats()
+    sampler = ClockSampler(_physical_gpu_index(local_rank))
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler.start()
+    out = greedy_decode_profiled(model, ids, torch.ones_like(ids), new, None, metrics, True)
+    sampler.stop()
+    v = torch.tensor([metrics.wall_prefill_ms, metrics.wall_decode_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms = float(v[0].item()), float(v[1].item())
+    # HBM bytes one decode step has to read on this GPU (last step's routing)
+    touched = 0
+    for ly in model.layers:
+        if ly.block is not None:
+            idx, _ = ly.block.topk(b_local)
+            own = ly.block.weights.slot_of_expert
+            touched += int(torch.unique(idx).numel()) if world == 1 else int((own >= 0).sum().item())
+    shape = cfg.moe
+    moe_layers = sum(1 for ly in model.layers if ly.block is not None)
+    kv_bytes = cfg.layers * b_local * (prompt + new) * cfg.n_kv_heads * (cfg.qk_dim + cfg.v_dim) * 2
+    attn_w = sum(sum(t.numel() * 2 for t in (getattr(ly, "wqkv", None), getattr(ly, "wq", None),
+                                             getattr(ly, "wkv_a", None), getattr(ly, "wkv_b", None), ly.wo)
+                     if t is not None) for ly in model.layers)
+    dense_w = sum(ly.dense_w13.numel() * 2 + ly.dense_w2.numel() * 2 for ly in model.layers if ly.block is None)
+    hbm = (touched * shape.routed_expert_bytes_bf16 + moe_layers * 3 * shape.hidden * shape.shared_inter * 2
+           + kv_bytes + attn_w + dense_w + cfg.vocab * cfg.hidden * 2)
+    floor_ms = hbm / (peaks["hbm_gbs"] * 1e9) * 1e3
+    steps = new - 1
+    if rank == 0:
+        emit({"metric": "model_decode_tokens_per_s", "value": (batch * new - batch) / (decode_ms * 1e-3),
+              "unit": "tokens/s", "n_gpus": world, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+              "config": {"workload": "%s, %d layers, %d sequences x %d random prompt ids (seed %d), %d greedy tokens, "
+                                     "random init" % (cfg.name, cfg.layers, batch, prompt, seed, new),
+                         "parallelism": "ep%d, sequences sharded %d per GPU, round-robin expert ownership" % (world, b_local),
+                         "launch_mode": "one CUDA-graph launch per decode step (all layers, lm_head, argmax)",
+                         "prefill_attention": "library fused attention over the cache, prompt in chunks of 4096 tokens"},
+              "prefill_ms": prefill_ms, "prefill_tokens_per_s": batch * prompt / (prefill_ms * 1e-3),
+              "decode_ms_per_step": decode_ms / steps,
+              "decode_hbm_roofline": {"bytes_per_step_per_gpu": hbm, "floor_ms": floor_ms, "peak_gbs": peaks["hbm_gbs"],
+                                      "frac": floor_ms / (decode_ms / steps),
+                                      "what": "weights of the experts a step touches (on this GPU), shared experts, "
+                                              "attention and dense weights, the cached keys/values, the lm_head"},
+              "generated_sample": out[0, prompt:prompt + 8].tolist(),
+              "clocks": sampler.summary()})
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_ours(args):
     from sparse_b200 import synth
     from sparse_b200.block import B200MoeBlock
@@ -1104,6 +1197,11 @@ def main():
     ap.add_argument("--placement", default="balanced",
                     help="expert placement at N>1: balanced (load-balanced replicated, default), rr "
                          "(round-robin) or perm:<seed> (seeded random permutation, one owner per expert)")
+    ap.add_argument("--model-decode", default="", choices=["", "qwen", "deepseek"],
+                    help="instead of the layer bench: prefill + greedy decode through the whole shaped model")
+    ap.add_argument("--model-batch", type=int, default=0)
+    ap.add_argument("--model-prompt", type=int, default=0)
+    ap.add_argument("--model-new", type=int, default=0)
     ap.add_argument("--cache-stress", action="store_true",
                     help="instead of the layer bench: decode steps at N>1 with non-owned experts cached locally "
                          "(owner / rr / rs / sparse)")
@@ -1122,6 +1220,9 @@ def main():
         return
     if args.cache_stress:
         cache_stress(args)
+        return
+    if args.model_decode:
+        model_decode(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)
