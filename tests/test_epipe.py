@@ -39,3 +39,42 @@ def test_rolling_gate_skips_after_a_dry_window():
     for i in range(8):
         assert g2.should_attempt()
         g2.record(i % 4 == 0)
+
+
+def test_scans_make_the_reference_decisions():
+    """400 cases recorded by calling the reference's own
+    `_try_execute_local_recv_groups_epipe` and `..._epipe_rs_residual_scan`
+    (utils/eval_core.py:11867-12512) on a stand-in object
+    (tests/golden/make_epipe_golden.py): whether EPIPE triggers, which expert is
+    overlapped with the ready ones, what runs before and after it."""
+    import json
+    import os
+    from sparse_b200.epipe import plan_residual_scan, plan_upfront_scan
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "epipe_golden.json")
+    with open(path) as fh:
+        cases = json.load(fh)
+    assert len(cases) == 400
+    triggered = 0
+    for c in cases:
+        needed = [s[0] for s in c["segments"]]
+        resident, pending = set(c["resident"]), set(c["pending"])
+        if c["scan"] == "upfront":
+            plan = plan_upfront_scan(needed, lambda e: e in resident)
+        else:
+            plan = plan_residual_scan(needed, lambda e: e in resident, lambda e: e in pending)
+        assert (plan is None) == c["fell_back"], c
+        if plan is None:
+            continue
+        triggered += 1
+        order = c["order"]
+        n_first = len(plan.first)
+        # the reference computes the ready segments first (one by one; here one grouped launch) ...
+        assert sorted(order[:n_first]) == sorted(plan.first), c
+        # ... then the overlapped expert, then the others in segment order
+        assert order[n_first] == plan.residual, c
+        assert order[n_first + 1:] == plan.rest, c
+        if c["staged"]:
+            assert plan.residual_kind == "demand" and c["staged"] == [plan.residual], c
+        else:
+            assert plan.residual_kind == "late", c
+    assert triggered > 200
