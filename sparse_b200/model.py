@@ -200,12 +200,18 @@ class ShapedMoeModel:
                                  cfg.v_dim, cfg.rope_dim, cfg.rope_theta, self.max_seq, ly.cache_k.data_ptr(),
                                  ly.cache_v.data_ptr(), self._s()), "sb_rope_append")
 
+    # When set to a list, every MoE call appends (layer index, input rows, chosen experts):
+    # what `rs_train.collect_pairs` turns into predictor training data.
+    trace = None
+
     def _mlp(self, ly: _Layer, x: torch.Tensor) -> torch.Tensor:
         if ly.block is None:
             out, _ = ops.grouped_swiglu(x, ly.dense_w13, ly.dense_w2, dense_rows=x.shape[0])
             return out[:x.shape[0]]
         out = torch.empty_like(x)
         ly.block.forward_device(x, out)
+        if self.trace is not None:
+            self.trace.append((self.layers.index(ly), x.clone(), ly.block.topk(x.shape[0])[0].clone()))
         return out
 
     # -- prefill -----------------------------------------------------------------------------

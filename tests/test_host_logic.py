@@ -180,3 +180,30 @@ def test_balanced_replicated_placement_spreads_a_hot_expert():
         for e, d in enumerate(p.assignment(0, s, "prefill")):
             per_rank[d] += load[0][e] / 4
     assert max(per_rank) < 0.45 * sum(per_rank)
+
+
+def test_rs_trainer_learns_a_routing_function_and_writes_loadable_checkpoints(tmp_path):
+    """`rs_train` on data whose next-layer routing is a fixed function of the
+    input: recall far above chance, and the checkpoint it writes is read back by
+    the serving-side loader with identical outputs."""
+    import torch
+    from sparse_b200 import rs, rs_train
+    torch.manual_seed(0)
+    n, h, e, k = 3000, 32, 12, 2
+    x = torch.randn(n, h)
+    w = torch.randn(e, h)
+    ids = torch.topk(x @ w.t(), k, dim=-1).indices
+    pairs = {(0, 1): (x, ids), (1, 2): (x, ids.flip(1))}
+    rows = rs_train.train_bank(pairs, str(tmp_path), e, hidden_dim=64, num_hidden_layers=1, epochs=25,
+                               device=torch.device("cpu"), eval_ks=(2, 4))
+    assert [r["target_layer"] for r in rows] == [1, 2]
+    chance = 4 / e
+    assert all(r["recall@4"] > 0.75 > chance for r in rows), rows
+    bank, task, layout, sources, missing = rs.load_rs_bank(str(tmp_path), 3, h, e, torch.device("cpu"), False)
+    assert task == "router_prob" and layout == "next_layer" and sources[1:] == [0, 1] and not missing
+    mod, _ = rs_train.train_pair(x[:200], ids[:200], e, 64, 1, epochs=1, device=torch.device("cpu"))
+    payload = torch.load(rows[0]["ckpt"], map_location="cpu", weights_only=False)
+    assert payload["label_type"] == "next_layer_true_router_topk_multihot" and payload["lead_layers"] == 1
+    probs = bank[1](x[:50])
+    assert probs.shape == (50, e) and torch.allclose(probs.sum(-1), torch.ones(50), atol=1e-5)
+    assert rs_train.recall_at_k(probs, ids[:50], 4) > 0.7
