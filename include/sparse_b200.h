@@ -223,11 +223,13 @@ int32_t sb_grouped_swiglu(const void *rows, const int32_t *tile_table,
  * address (`row_dst` uint64 [rows of the tile table], 0 = drop) instead of into
  * a dense output buffer: rows of the local expert sort go straight to the rows
  * of a return buffer that a later sb_combine reads (see
- * sb_ep_exchange_dispatch_local).  Groups of any size (swept 16 rows at a time). */
+ * sb_ep_exchange_dispatch_local).  Groups of any size (swept 16 rows at a time).
+ * `T` is the caller's token count of this step (it selects the same K split,
+ * hence the same summation order, as the step's other launches). */
 int32_t sb_decode_experts_to(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
                              const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                              const void *w2, const void *row_scale, int32_t H, int32_t I, int32_t n_slots,
-                             void *hbuf, const uint64_t *row_dst, int32_t *status, void *stream);
+                             void *hbuf, const uint64_t *row_dst, int32_t T, int32_t *status, void *stream);
 
 /* sb_grouped_swiglu restricted to one of its two passes: `passes` 1 = gate/up +
  * SwiGLU into `hbuf`, 2 = down projection from `hbuf` into `out`, 3 = both.
@@ -551,8 +553,12 @@ int32_t sb_moe_layer_forward(const sb_moe_layer *layer, int32_t *status, void *s
  *                  rounded to bf16) on q [T,n_q,dk] in place and on k
  *                  [T,n_kv,dk]; rotated k and v [T,n_kv,dv] are stored into the
  *                  cache rows (seq_of_token[t], pos_of_token[t]) of cache_k
- *                  [B,s_max,n_kv,dk] / cache_v [B,s_max,n_kv,dv].
- * sb_attn_decode   one query per sequence, q [B,n_q,dk], against the first
+ *                  [B,s_max,n_kv,dk] / cache_v [B,s_max,n_kv,dv].  q_stride,
+ *                  k_stride, v_stride: elements between consecutive tokens
+ *                  (0 = densely packed), so q, k, v may be column slices of
+ *                  one fused projection output.
+ * sb_attn_decode   one query per sequence, q [B,n_q,dk] (q_stride elements
+ *                  between sequences, 0 = packed), against the first
  *                  seq_lens[b] (device int32) cached positions; softmax in fp32;
  *                  out [B,n_q,dv].  The keys are split `n_split` ways over CTAs
  *                  and merged by a second kernel; ws needs
@@ -563,11 +569,13 @@ int32_t sb_add_rmsnorm(void *residual, const void *delta, const void *delta2, co
                        int32_t T, int32_t H, void *out, void *stream);
 int32_t sb_rope_append(void *q, const void *k, const void *v, const int32_t *seq_of_token,
                        const int32_t *pos_of_token, int32_t T, int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv,
-                       int32_t rope_dim, float theta, int32_t s_max, void *cache_k, void *cache_v, void *stream);
+                       int32_t rope_dim, float theta, int32_t s_max, void *cache_k, void *cache_v, int32_t q_stride,
+                       int32_t k_stride, int32_t v_stride, void *stream);
 size_t sb_attn_decode_workspace_bytes(int32_t B, int32_t n_q, int32_t dv, int32_t n_split);
-int32_t sb_attn_decode(const void *q, const void *cache_k, const void *cache_v, const int32_t *seq_lens, int32_t B,
-                       int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv, int32_t s_max, float scale,
-                       int32_t n_split, void *ws, size_t ws_bytes, void *out, void *stream);
+int32_t sb_attn_decode(const void *q, int32_t q_stride, const void *cache_k, const void *cache_v,
+                       const int32_t *seq_lens, int32_t B, int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv,
+                       int32_t s_max, float scale, int32_t n_split, void *ws, size_t ws_bytes, void *out,
+                       void *stream);
 
 /* Number of kernels the last sb_moe_layer_forward of this thread launched. */
 int32_t sb_last_launch_count(void);

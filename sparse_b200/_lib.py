@@ -59,7 +59,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu": (i32, [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_decode_experts": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32,
                                 vp, vp, vp, vp]),
-    "sb_decode_experts_to": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp]),
+    "sb_decode_experts_to": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp]),
     "sb_grouped_swiglu_mixed": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp,
                                       i32, i32, vp, vp, vp, vp, vp]),
     "sb_route_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
@@ -90,9 +90,10 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_grouped_swiglu_scatter": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
     "sb_ep_combine": (i32, [C.POINTER(vp), vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "sb_add_rmsnorm": (i32, [vp, vp, vp, vp, C.c_float, i32, i32, vp, vp]),
-    "sb_rope_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp, vp, vp]),
+    "sb_rope_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp, vp, i32, i32, i32,
+                             vp]),
     "sb_attn_decode_workspace_bytes": (sz, [i32, i32, i32, i32]),
-    "sb_attn_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp, sz, vp, vp]),
+    "sb_attn_decode": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, C.c_float, i32, vp, sz, vp, vp]),
     "sb_moe_layer_struct_bytes": (sz, []),
     "sb_moe_layer_workspace_bytes": (sz, [i32, i32, i32, i32, i32, i32]),
     "sb_moe_layer_forward": (i32, [C.POINTER(MoeLayer), vp, vp]),

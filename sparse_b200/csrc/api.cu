@@ -323,10 +323,10 @@ int32_t sb_decode_experts(const void *x, const int32_t *item_of_slot, int32_t it
 int32_t sb_decode_experts_to(const void *x, const int32_t *item_of_slot, int32_t items_per_row,
                              const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                              const void *w2, const void *row_scale, int32_t H, int32_t I, int32_t n_slots,
-                             void *hbuf, const uint64_t *row_dst, int32_t *status, void *stream) {
-  if (!tile_table || !row_dst) return fail(SB_E_INVALID_ARG, "sb_decode_experts_to: null pointer");
+                             void *hbuf, const uint64_t *row_dst, int32_t T, int32_t *status, void *stream) {
+  if (!tile_table || !row_dst || T < 1) return fail(SB_E_INVALID_ARG, "sb_decode_experts_to: bad arguments");
   return launch_decode_experts(x, item_of_slot, items_per_row, tile_table, slot_of_expert, w13, w2, row_scale, H,
-                               I, n_slots, hbuf, nullptr, nullptr, nullptr, nullptr, 0, 1, nullptr, nullptr, status,
+                               I, n_slots, hbuf, nullptr, nullptr, nullptr, nullptr, 0, T, nullptr, nullptr, status,
                                2, 1 << 30, nullptr, reinterpret_cast<const unsigned long long *>(row_dst),
                                static_cast<cudaStream_t>(stream));
 }

@@ -316,6 +316,10 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
   // elements, 1 for 44, 4 for 176 beat finer splits by up to 8 % at 8 tokens)
   auto slices = [](int k) { const int ch = k / 32; return ch > 128 ? 4 : ch > 48 ? 2 : 1; };
   const int ks1 = slices(H), ks2_routed = slices(I), ks2_shared = slices(I_sh > 0 ? I_sh : I);
+  // (Splitting K finer at one or two tokens, so that the 352 pass-1 / 128 pass-2
+  // tasks of a single token spread over all CTAs in several small rounds, was
+  // measured slower on B200: 50 us against 45 us per layer at one token.  The
+  // per-task reduction and synchronisation cost more than the emptier round.)
   // Next to the tile kernel (ctas_per_sm == 1) the SM must already be in the
   // large-shared-memory configuration that kernel needs, or the two could not
   // share an SM; alone, the default split leaves more L1 for the token rows.

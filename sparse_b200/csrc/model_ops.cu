@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(128)
 rope_append_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ k,
                    const __nv_bfloat16 *__restrict__ v, const int32_t *__restrict__ seq_of_token,
                    const int32_t *__restrict__ pos_of_token, int n_q, int n_kv, int dk, int dv, int rope_dim,
-                   float theta, int s_max, __nv_bfloat16 *__restrict__ cache_k, __nv_bfloat16 *__restrict__ cache_v) {
+                   float theta, int s_max, __nv_bfloat16 *__restrict__ cache_k, __nv_bfloat16 *__restrict__ cache_v,
+                   int q_stride, int k_stride, int v_stride) {
   const int t = blockIdx.x;
   const int pos = pos_of_token[t], seq = seq_of_token[t];
   const int half = rope_dim >> 1;
@@ -93,7 +94,7 @@ rope_append_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restric
     float sn, cs;
     sincosf(ang, &sn, &cs);
     sn = round_bf16(sn); cs = round_bf16(cs);
-    __nv_bfloat16 *p = q + ((size_t)t * n_q + h) * dk;
+    __nv_bfloat16 *p = q + (size_t)t * q_stride + (size_t)h * dk;
     const float a = __bfloat162float(p[j]), b = __bfloat162float(p[j + half]);
     p[j] = __float2bfloat16_rn(round_bf16(a * cs) + round_bf16(-b * sn));
     p[j + half] = __float2bfloat16_rn(round_bf16(b * cs) + round_bf16(a * sn));
@@ -103,7 +104,7 @@ rope_append_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restric
   __nv_bfloat16 *cv = cache_v + ((size_t)seq * s_max + pos) * n_kv * dv;
   for (int i = threadIdx.x; i < n_kv * dk; i += blockDim.x) {
     const int h = i / dk, j = i - h * dk;
-    const __nv_bfloat16 *p = k + ((size_t)t * n_kv + h) * dk;
+    const __nv_bfloat16 *p = k + (size_t)t * k_stride + (size_t)h * dk;
     float val = __bfloat162float(p[j]);
     if (j < rope_dim) {
       const int jj = j < half ? j : j - half;
@@ -116,7 +117,7 @@ rope_append_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restric
     }
     ck[i] = __float2bfloat16_rn(val);
   }
-  for (int i = threadIdx.x; i < n_kv * dv; i += blockDim.x) cv[i] = v[(size_t)t * n_kv * dv + i];
+  for (int i = threadIdx.x; i < n_kv * dv; i += blockDim.x) cv[i] = v[(size_t)t * v_stride + i];
 }
 
 // Decode attention, split over the keys.  grid = (sequences * query heads,
@@ -125,10 +126,11 @@ rope_append_kernel(__nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restric
 // per warp; the warps and then the splits are merged by their running maxima.
 template <int DK, int DV>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ cache_k,
+attn_decode_kernel(const __nv_bfloat16 *__restrict__ q, int q_stride, const __nv_bfloat16 *__restrict__ cache_k,
                    const __nv_bfloat16 *__restrict__ cache_v, const int32_t *__restrict__ seq_lens, int n_q,
                    int n_kv, int s_max, float scale, int n_split, float *__restrict__ part) {
   constexpr int EK = DK / 32, EV = DV / 32;
+  constexpr int U = 4;                        // keys a warp has in flight per iteration
   const int bh = blockIdx.x, split = blockIdx.y;
   const int b = bh / n_q, h = bh - b * n_q;
   const int hk = h / (n_q / n_kv);
@@ -138,26 +140,48 @@ attn_decode_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__r
   const int j0 = split * per, j1 = min(len, j0 + per);
   float qv[EK];
 #pragma unroll
-  for (int e = 0; e < EK; ++e) qv[e] = __bfloat162float(q[((size_t)b * n_q + h) * DK + lane * EK + e]) * scale;
+  for (int e = 0; e < EK; ++e)
+    qv[e] = __bfloat162float(q[(size_t)b * q_stride + (size_t)h * DK + lane * EK + e]) * scale;
   float m = -INFINITY, l = 0.f, acc[EV];
 #pragma unroll
   for (int e = 0; e < EV; ++e) acc[e] = 0.f;
   const __nv_bfloat16 *kb = cache_k + ((size_t)b * s_max * n_kv + hk) * DK + lane * EK;
   const __nv_bfloat16 *vb = cache_v + ((size_t)b * s_max * n_kv + hk) * DV + lane * EV;
-  for (int j = j0 + warp; j < j1; j += 4) {
-    const __nv_bfloat16 *kp = kb + (size_t)j * n_kv * DK;
-    const __nv_bfloat16 *vp = vb + (size_t)j * n_kv * DV;
-    float s = 0.f, kv[EK], vv[EV];
-    load_bf16<EK>(kp, kv);
-    load_bf16<EV>(vp, vv);
+  for (int j = j0 + warp * U; j < j1; j += 4 * U) {
+    float kv[U][EK], vv[U][EV], s[U];
 #pragma unroll
-    for (int e = 0; e < EK; ++e) s += qv[e] * kv[e];
-    s = warp_sum(s);
-    const float m_new = fmaxf(m, s);
-    const float corr = __expf(m - m_new), p = __expf(s - m_new);
-    l = l * corr + p;
+    for (int u = 0; u < U; ++u) {
+      const int jj = min(j + u, j1 - 1);       // clamped: the duplicate is masked below
+      load_bf16<EK>(kb + (size_t)jj * n_kv * DK, kv[u]);
+      load_bf16<EV>(vb + (size_t)jj * n_kv * DV, vv[u]);
+    }
 #pragma unroll
-    for (int e = 0; e < EV; ++e) acc[e] = acc[e] * corr + p * vv[e];
+    for (int u = 0; u < U; ++u) {
+      s[u] = 0.f;
+#pragma unroll
+      for (int e = 0; e < EK; ++e) s[u] += qv[e] * kv[u][e];
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+      for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], off);
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (j + u >= j1) s[u] = -INFINITY;
+      m_new = fmaxf(m_new, s[u]);
+    }
+    const float corr = __expf(m - m_new);
+    l *= corr;
+#pragma unroll
+    for (int e = 0; e < EV; ++e) acc[e] *= corr;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float p = __expf(s[u] - m_new);    // exp(-inf) = 0 for the masked keys
+      l += p;
+#pragma unroll
+      for (int e = 0; e < EV; ++e) acc[e] += p * vv[u][e];
+    }
     m = m_new;
   }
   // merge the four warps
@@ -227,7 +251,13 @@ int32_t sb_add_rmsnorm(void *residual, const void *delta, const void *delta2, co
 
 int32_t sb_rope_append(void *q, const void *k, const void *v, const int32_t *seq_of_token,
                        const int32_t *pos_of_token, int32_t T, int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv,
-                       int32_t rope_dim, float theta, int32_t s_max, void *cache_k, void *cache_v, void *stream) {
+                       int32_t rope_dim, float theta, int32_t s_max, void *cache_k, void *cache_v, int32_t q_stride,
+                       int32_t k_stride, int32_t v_stride, void *stream) {
+  if (q_stride == 0) q_stride = n_q * dk;
+  if (k_stride == 0) k_stride = n_kv * dk;
+  if (v_stride == 0) v_stride = n_kv * dv;
+  if (q_stride < n_q * dk || k_stride < n_kv * dk || v_stride < n_kv * dv)
+    return fail(SB_E_INVALID_ARG, "sb_rope_append: a token stride is smaller than the token");
   if (T < 0 || n_q < 1 || n_kv < 1 || dk < 2 || dv < 1 || rope_dim < 0 || rope_dim > dk || (rope_dim & 1) || s_max < 1)
     return fail(SB_E_INVALID_ARG, "sb_rope_append: bad shape");
   if (T == 0) return SB_OK;
@@ -236,7 +266,7 @@ int32_t sb_rope_append(void *q, const void *k, const void *v, const int32_t *seq
   rope_append_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16 *>(q), static_cast<const __nv_bfloat16 *>(k), static_cast<const __nv_bfloat16 *>(v),
       seq_of_token, pos_of_token, n_q, n_kv, dk, dv, rope_dim, theta, s_max,
-      static_cast<__nv_bfloat16 *>(cache_k), static_cast<__nv_bfloat16 *>(cache_v));
+      static_cast<__nv_bfloat16 *>(cache_k), static_cast<__nv_bfloat16 *>(cache_v), q_stride, k_stride, v_stride);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -246,9 +276,12 @@ size_t sb_attn_decode_workspace_bytes(int32_t B, int32_t n_q, int32_t dv, int32_
   return (size_t)B * n_q * n_split * (dv + 2) * sizeof(float);
 }
 
-int32_t sb_attn_decode(const void *q, const void *cache_k, const void *cache_v, const int32_t *seq_lens, int32_t B,
-                       int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv, int32_t s_max, float scale,
-                       int32_t n_split, void *ws, size_t ws_bytes, void *out, void *stream) {
+int32_t sb_attn_decode(const void *q, int32_t q_stride, const void *cache_k, const void *cache_v,
+                       const int32_t *seq_lens, int32_t B, int32_t n_q, int32_t n_kv, int32_t dk, int32_t dv,
+                       int32_t s_max, float scale, int32_t n_split, void *ws, size_t ws_bytes, void *out,
+                       void *stream) {
+  if (q_stride == 0) q_stride = n_q * dk;
+  if (q_stride < n_q * dk) return fail(SB_E_INVALID_ARG, "sb_attn_decode: q_stride smaller than a token's heads");
   if (B < 0 || n_q < 1 || n_kv < 1 || n_q % n_kv != 0 || s_max < 1 || n_split < 1 || n_split > 256)
     return fail(SB_E_INVALID_ARG, "sb_attn_decode: bad shape");
   if (B == 0) return SB_OK;
@@ -263,15 +296,15 @@ int32_t sb_attn_decode(const void *q, const void *cache_k, const void *cache_v, 
   float *part = static_cast<float *>(ws);
   __nv_bfloat16 *oo = static_cast<__nv_bfloat16 *>(out);
   if (dk == 128 && dv == 128) {
-    attn_decode_kernel<128, 128><<<grid, 128, 0, st>>>(qq, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
+    attn_decode_kernel<128, 128><<<grid, 128, 0, st>>>(qq, q_stride, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
     SB_LAUNCH_CHECK();
     attn_merge_kernel<128><<<B * n_q, 128, 0, st>>>(part, n_split, oo);
   } else if (dk == 192 && dv == 128) {
-    attn_decode_kernel<192, 128><<<grid, 128, 0, st>>>(qq, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
+    attn_decode_kernel<192, 128><<<grid, 128, 0, st>>>(qq, q_stride, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
     SB_LAUNCH_CHECK();
     attn_merge_kernel<128><<<B * n_q, 128, 0, st>>>(part, n_split, oo);
   } else if (dk == 64 && dv == 64) {
-    attn_decode_kernel<64, 64><<<grid, 128, 0, st>>>(qq, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
+    attn_decode_kernel<64, 64><<<grid, 128, 0, st>>>(qq, q_stride, kk, vv, seq_lens, n_q, n_kv, s_max, scale, n_split, part);
     SB_LAUNCH_CHECK();
     attn_merge_kernel<64><<<B * n_q, 128, 0, st>>>(part, n_split, oo);
   } else {

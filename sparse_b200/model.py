@@ -151,7 +151,10 @@ class ShapedMoeModel:
                                         fp32_router_logits=cfg.attention == "mla", ep_rank=ep_rank, ep_size=ep_size,
                                         process_group=process_group, owner=owner)
             self.layers.append(ly)
-        self.n_split = max(1, min(64, (2 * 148 + batch * nh - 1) // (batch * nh)))
+        # enough key splits for about six CTAs per SM: a CTA streams its keys with
+        # a few hundred bytes in flight per warp, so bandwidth comes from CTA count
+        sms = max(1, int(lib.sb_device_sm_count()) or 148)
+        self.n_split = max(1, min(64, (6 * sms + batch * nh - 1) // (batch * nh)))
         ws = lib.sb_attn_decode_workspace_bytes(batch, nh, dv, self.n_split)
         self.attn_ws = torch.empty((ws,), dtype=torch.uint8, device=device)
         # decode-step state advanced by the graph itself
@@ -178,27 +181,26 @@ class ShapedMoeModel:
         nh, nkv, dk, dv, t = cfg.n_heads, cfg.n_kv_heads, cfg.qk_dim, cfg.v_dim, x.shape[0]
         if cfg.attention == "mla":
             nope, rope = dk - cfg.rope_dim, cfg.rope_dim
-            q = F.linear(x, ly.wq).view(t, nh, dk)                    # per head: [rope | nope]
+            q = F.linear(x, ly.wq)                                     # per head: [rope | nope]
             kv_a = F.linear(x, ly.wkv_a)
             c_kv = kv_a[:, :cfg.kv_lora_rank].contiguous()
             k_pe = kv_a[:, cfg.kv_lora_rank:]
             c_kv = self._norm(c_kv, None, ly.kv_norm)
             kv = F.linear(c_kv, ly.wkv_b).view(t, nh, nope + dv)
-            k = torch.cat([k_pe.unsqueeze(1).expand(t, nh, rope), kv[:, :, :nope]], dim=2).contiguous()
-            v = kv[:, :, nope:].contiguous()
-            return q.contiguous(), k, v
+            k = torch.cat([k_pe.unsqueeze(1).expand(t, nh, rope), kv[:, :, :nope]], dim=2).reshape(t, nh * dk)
+            v = kv[:, :, nope:].reshape(t, nh * dv)
+            return q, k, v
+        # column slices of the fused projection: the kernels take the token stride
         qkv = F.linear(x, ly.wqkv, ly.bqkv)
-        q = qkv[:, :nh * dk].contiguous().view(t, nh, dk)
-        k = qkv[:, nh * dk:nh * dk + nkv * dk].contiguous().view(t, nkv, dk)
-        v = qkv[:, nh * dk + nkv * dk:].contiguous().view(t, nkv, dv)
-        return q, k, v
+        return qkv[:, :nh * dk], qkv[:, nh * dk:nh * dk + nkv * dk], qkv[:, nh * dk + nkv * dk:]
 
     def _rope_append(self, ly: _Layer, q, k, v, seq_of_token, pos_of_token) -> None:
         cfg = self.cfg
         check(lib.sb_rope_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), seq_of_token.data_ptr(),
                                  pos_of_token.data_ptr(), q.shape[0], cfg.n_heads, cfg.n_kv_heads, cfg.qk_dim,
                                  cfg.v_dim, cfg.rope_dim, cfg.rope_theta, self.max_seq, ly.cache_k.data_ptr(),
-                                 ly.cache_v.data_ptr(), self._s()), "sb_rope_append")
+                                 ly.cache_v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), self._s()),
+              "sb_rope_append")
 
     # When set to a list, every MoE call appends (layer index, input rows, chosen experts):
     # what `rs_train.collect_pairs` turns into predictor training data.
@@ -234,7 +236,7 @@ class ShapedMoeModel:
             x = self._norm(resid, delta, ly.ln1)
             q, k, v = self._qkv(ly, x)
             self._rope_append(ly, q, k, v, seq, pos)
-            qh = q.view(b, tc, nh, dk).transpose(1, 2)
+            qh = q.reshape(b, tc, nh, dk).transpose(1, 2)
             kh = ly.cache_k[:b, :kv_len].transpose(1, 2)
             vh = ly.cache_v[:b, :kv_len].transpose(1, 2)
             if nkv != nh:
@@ -281,7 +283,7 @@ class ShapedMoeModel:
             q, k, v = self._qkv(ly, x)
             self._rope_append(ly, q, k, v, self.seq_ids, self.cur_pos)
             att = torch.empty((b, nh * dv), dtype=torch.bfloat16, device=self.device)
-            check(lib.sb_attn_decode(q.data_ptr(), ly.cache_k.data_ptr(), ly.cache_v.data_ptr(),
+            check(lib.sb_attn_decode(q.data_ptr(), q.stride(0), ly.cache_k.data_ptr(), ly.cache_v.data_ptr(),
                                      self.seq_lens.data_ptr(), b, nh, nkv, dk, dv, self.max_seq,
                                      1.0 / math.sqrt(dk), self.n_split, self.attn_ws.data_ptr(),
                                      self.attn_ws.numel(), att.data_ptr(), self._s()), "sb_attn_decode")

@@ -317,7 +317,7 @@ class LocalCacheEpLayer(ExpertParallelLayer):
                 check(lib.sb_decode_experts_to(
                     x.data_ptr(), r.item_of_slot.data_ptr(), k, r.local_tiles.data_ptr(),
                     self.local_slots.data_ptr(), w.w13.data_ptr(), w.w2.data_ptr(), r.local_scale.data_ptr(),
-                    w.hidden, w.inter, w.n_slots, self.local_hbuf.data_ptr(), self.local_dst.data_ptr(),
+                    w.hidden, w.inter, w.n_slots, self.local_hbuf.data_ptr(), self.local_dst.data_ptr(), t,
                     r.status.data_ptr(), stream.cuda_stream), "sb_decode_experts_to")
                 r.launches += 2
             r.stage_experts_and_shared()

@@ -75,7 +75,7 @@ def test_rope_append(n_q, n_kv, dk, dv, rope_dim):
     want_k = _rope_ref(k, pos_d, rope_dim, 10000.0)
     qq = q.clone()
     check(lib.sb_rope_append(qq.data_ptr(), k.data_ptr(), v.data_ptr(), seq_d.data_ptr(), pos_d.data_ptr(), t, n_q,
-                             n_kv, dk, dv, rope_dim, 10000.0, s_max, ck.data_ptr(), cv.data_ptr(), _stream()),
+                             n_kv, dk, dv, rope_dim, 10000.0, s_max, ck.data_ptr(), cv.data_ptr(), 0, 0, 0, _stream()),
           "sb_rope_append")
     torch.cuda.synchronize()
     # sin/cos of the device's fast path against libm's: a bf16 step on a few elements at most
@@ -102,7 +102,7 @@ def test_attn_decode(n_q, n_kv, dk, dv, lens, n_split):
     ws = torch.empty(lib.sb_attn_decode_workspace_bytes(b, n_q, dv, n_split), dtype=torch.uint8, device=DEV)
     out = torch.empty(b, n_q, dv, dtype=bf, device=DEV)
     scale = 1.0 / math.sqrt(dk)
-    check(lib.sb_attn_decode(q.data_ptr(), ck.data_ptr(), cv.data_ptr(), seq_lens.data_ptr(), b, n_q, n_kv, dk, dv,
+    check(lib.sb_attn_decode(q.data_ptr(), 0, ck.data_ptr(), cv.data_ptr(), seq_lens.data_ptr(), b, n_q, n_kv, dk, dv,
                              s_max, scale, n_split, ws.data_ptr(), ws.numel(), out.data_ptr(), _stream()),
           "sb_attn_decode")
     torch.cuda.synchronize()
@@ -118,6 +118,39 @@ def test_attn_decode(n_q, n_kv, dk, dv, lens, n_split):
         got = out[i].float()
         assert float((got - want).abs().max()) < 2e-2
         assert float((got - want).norm() / want.norm()) < 5e-3
+
+
+def test_kernels_take_column_slices_of_a_fused_projection():
+    """q, k, v as strided column slices of one [T, q+k+v] buffer give the bits of packed tensors."""
+    torch.manual_seed(4)
+    bf = torch.bfloat16
+    n_q, n_kv, dk, dv, t, b, s_max = 4, 2, 64, 64, 5, 5, 16
+    fused = torch.randn(t, n_q * dk + n_kv * dk + n_kv * dv).to(bf).to(DEV)
+    q, k, v = fused[:, :n_q * dk], fused[:, n_q * dk:n_q * dk + n_kv * dk], fused[:, n_q * dk + n_kv * dk:]
+    seq = torch.arange(t, dtype=torch.int32, device=DEV)
+    pos = torch.full((t,), 3, dtype=torch.int32, device=DEV)
+    outs = []
+    for packed in (False, True):
+        buf = fused.clone()
+        qq = buf[:, :n_q * dk]
+        kk, vv = buf[:, n_q * dk:n_q * dk + n_kv * dk], buf[:, n_q * dk + n_kv * dk:]
+        if packed:
+            qq, kk, vv = qq.contiguous(), kk.contiguous(), vv.contiguous()
+        ck = torch.zeros(b, s_max, n_kv, dk, dtype=bf, device=DEV)
+        cv = torch.zeros(b, s_max, n_kv, dv, dtype=bf, device=DEV)
+        check(lib.sb_rope_append(qq.data_ptr(), kk.data_ptr(), vv.data_ptr(), seq.data_ptr(), pos.data_ptr(), t, n_q,
+                                 n_kv, dk, dv, dk, 10000.0, s_max, ck.data_ptr(), cv.data_ptr(), qq.stride(0),
+                                 kk.stride(0), vv.stride(0), _stream()), "sb_rope_append")
+        lens = torch.full((b,), 4, dtype=torch.int32, device=DEV)
+        ws = torch.empty(lib.sb_attn_decode_workspace_bytes(b, n_q, dv, 2), dtype=torch.uint8, device=DEV)
+        out = torch.empty(b, n_q * dv, dtype=bf, device=DEV)
+        check(lib.sb_attn_decode(qq.data_ptr(), qq.stride(0), ck.data_ptr(), cv.data_ptr(), lens.data_ptr(), b, n_q,
+                                 n_kv, dk, dv, s_max, 0.125, 2, ws.data_ptr(), ws.numel(), out.data_ptr(), _stream()),
+              "sb_attn_decode")
+        torch.cuda.synchronize()
+        outs.append((qq.clone().contiguous(), ck.clone(), cv.clone(), out.clone()))
+    for a, c in zip(outs[0], outs[1]):
+        assert torch.equal(a, c)
 
 
 def _tiny_model(batch, max_seq, **kw):
