@@ -13,6 +13,8 @@
 // chunk by warp match) -> gather (one warp per output row, 16-byte vectors).
 // The gather is the only HBM-heavy part: it reads T*H*2 bytes (re-reads of a
 // row hit L2) and writes n_items*H*2.
+#include <atomic>
+
 #include "sb_common.cuh"
 
 namespace sb {
@@ -341,7 +343,9 @@ static __device__ __align__(256) int32_t g_permute_scratch[kStaticScratchInts];
 // Device address of g_permute_scratch per device ordinal (0 = not looked up yet).
 // In host code the symbol's name is only a handle; the address a kernel can use
 // has to be asked for, with that device current.
-static int32_t *g_permute_scratch_addr[64];
+// Two host threads making the first call on a device both store the same value;
+// the atomic makes that a defined (relaxed) access instead of a data race.
+static std::atomic<int32_t *> g_permute_scratch_addr[64];
 
 extern "C" int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
                                       const void *item_scale, int32_t n_items,
@@ -362,19 +366,21 @@ extern "C" int32_t sb_permute_noalloc(const void *x, const int32_t *item_expert,
   int dev = -1;
   SB_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return sb::fail(SB_E_UNSUPPORTED, "sb_permute_noalloc: device ordinal %d", dev);
-  if (g_permute_scratch_addr[dev] == nullptr) {
+  int32_t *scratch = g_permute_scratch_addr[dev].load(std::memory_order_relaxed);
+  if (scratch == nullptr) {
     int32_t *p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_permute_scratch);
     if (e != cudaSuccess || p == nullptr)
       return sb::fail(SB_E_CUDA, "sb_permute_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
                       cudaGetErrorString(e));
-    g_permute_scratch_addr[dev] = p;
+    g_permute_scratch_addr[dev].store(p, std::memory_order_relaxed);
+    scratch = p;
   }
   // Nothing in the scratch has to start at zero: the count pass overwrites every
   // histogram cell the later passes read, so stale contents of an earlier call
   // are never observed.
   return sb::launch_permute(x, item_expert, item_scale, n_items, items_per_row, H, E,
-                            g_permute_scratch_addr[dev],
+                            scratch,
                             (size_t)kStaticScratchInts * sizeof(int32_t), out_rows, expert_offsets,
                             slot_of_item, item_of_slot, slot_scale, tile_table,
                             static_cast<cudaStream_t>(stream));
