@@ -1047,6 +1047,19 @@ def run_ours(args):
         gemm_all[rank] = my_gemm
         dist.all_reduce(gemm_all)
         rank_skew = {"received_rows": rows_all.tolist(), "routed_gemm_ms": [round(v, 4) for v in gemm_all.tolist()]}
+        # where the two streams stand when, in the real (overlapped, eagerly launched) schedule of rank 0
+        ep_layer.timeline = []
+        for i in range(reps):
+            step_dev(i)
+        barrier()
+        tl = ep_layer.timeline
+        ep_layer.timeline = None
+        per_tl = len(tl) // reps
+        ep_timeline = {}
+        for rep in range(1, reps):                         # the first pass warms the eager path up
+            chunk = tl[rep * per_tl:(rep + 1) * per_tl]
+            for name, ev in chunk[1:]:
+                ep_timeline[name] = ep_timeline.get(name, 0.0) + chunk[0][1].elapsed_time(ev) / (reps - 1)
 
     # ---- decode-sized steps through the same block (all ranks) ----
     decode = {}
@@ -1145,6 +1158,7 @@ def run_ours(args):
         if ep_parity is not None:
             line["ep_parity"] = ep_parity
             line["rank_skew"] = rank_skew
+            line["ep_timeline_ms"] = {k: round(v, 4) for k, v in ep_timeline.items()}
         if other_placements:
             line["placements"] = other_placements
         if decode:

@@ -68,10 +68,10 @@ int32_t sb_init(int32_t device);
 
 /* Process-wide scheduling knobs of the kernels, read at every launch; results
  * are bit-identical under every setting, only the time changes.
- *   "sched"          0 = walk the tile table in order with a fixed stride,
- *                    1 = rank the row chunks by size and deal them out
- *                        boustrophedon, 2 = as 1 with odd CTA pairs walking
- *                        their list backwards (default)
+ *   "sched"          0 = walk the tile table in order with a fixed stride
+ *                        (default), 1 = rank the row chunks by the size of
+ *                        their expert and deal them out boustrophedon, 2 = as
+ *                        1 with odd CTA pairs walking their list backwards
  *   "dense_group"    row chunks per raster block of a dense (shared-expert)
  *                    pass, 1..64 (default 1)
  *   "router_overlap" 1 = sb_moe_layer_forward runs the router beside the shared

@@ -571,29 +571,48 @@ class ExpertParallelLayer:
                 # first with a pipeline one stage short, which leaves each SM room
                 # for one router CTA: the router's CUDA-core dot products run under
                 # the tensor-core pass, not in front of it.
+                tl = self.timeline
+
+                def stamp(name, st):
+                    if tl is not None:
+                        ev = torch.cuda.Event(enable_timing=True)
+                        ev.record(st)
+                        tl.append((name, ev))
+
                 r.begin(x)
                 has_shared = bool(r.w.shared_inter)
+                stamp("begin", stream)
                 self._fork.record(stream)
                 if has_shared:
                     r.stage_shared(1, stages=5)
+                    stamp("main: shared gate/up done", stream)
                 with torch.cuda.stream(self._side):
                     self._side.wait_event(self._fork)
                     r.stage_route()
+                    stamp("side: router+sort done", self._side)
                     self._mid.record(self._side)
                     r.stage_publish()
                     self._barrier()
+                    stamp("side: counts exchanged", self._side)
                     r.stage_plan()
                     r.stage_dispatch()
+                    stamp("side: rows dispatched", self._side)
                     self._barrier()
                     r.stage_resolve()
+                    stamp("side: rows landed", self._side)
                     self._join.record(self._side)
                 stream.wait_event(self._mid)            # the scalar gate of the shared expert is known
                 if has_shared:
                     r.stage_shared(2)
+                    stamp("main: shared down done", stream)
                 stream.wait_event(self._join)
             fused = marks is None          # the timing marks time the GEMM and the return push separately
             r.stage_experts(fused=fused)
             mark("routed_swiglu")
+            if self.timeline is not None and marks is None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                self.timeline.append(("main: routed GEMM + return done", ev))
             if not fused:
                 r.stage_return()
                 mark("return rows")
@@ -601,6 +620,10 @@ class ExpertParallelLayer:
             mark("barrier(outputs ready)")
             res = r.stage_combine(out)
             mark("combine")
+            if self.timeline is not None and marks is None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                self.timeline.append(("main: combined", ev))
         self.last_launches = r.launches
         return res
 
@@ -638,6 +661,9 @@ class ExpertParallelLayer:
 
     # When set to a list, forward() appends (stage name, CUDA event) marks to it.
     stage_events = None
+    # When set to a list, the overlapped (two-stream) path appends (point, CUDA event)
+    # stamps on both streams: where each stream stands when, in the real schedule.
+    timeline = None
 
     def check_status(self) -> None:
         self.r.check_status()

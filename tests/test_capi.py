@@ -67,3 +67,14 @@ def test_decode_limit_matches_header():
     text = open(os.path.join(ROOT, "include", "sparse_b200.h")).read()
     m = re.search(r"#define\s+SB_DECODE_MAX_TOKENS\s+(\d+)", text)
     assert m and int(m.group(1)) == _lib.DECODE_MAX_TOKENS
+
+
+def test_tuning_knob_argument_checks():
+    """No GPU needed: keys and ranges of sb_set_tuning."""
+    from sparse_b200 import _lib
+    lib = _lib.lib
+    assert lib.sb_set_tuning(b"sched", 0) == 0 and lib.sb_set_tuning(b"dense_group", 1) == 0
+    assert lib.sb_set_tuning(b"router_overlap", 1) == 0
+    for key, bad in ((b"sched", -1), (b"sched", 3), (b"dense_group", 0), (b"dense_group", 65), (b"router_overlap", 2)):
+        assert lib.sb_set_tuning(key, bad) != 0
+    assert lib.sb_set_tuning(b"unknown", 0) != 0 and lib.sb_set_tuning(None, 0) != 0

@@ -267,6 +267,49 @@ def test_grouped_swiglu_against_oracle(h, i, e, counts):
     assert float((got_h == want_h).float().mean()) > 0.9
 
 
+def test_tuning_knobs_change_the_schedule_not_the_bits():
+    """Every setting of sb_set_tuning gives bit-identical rows: tile walk (table
+    order, ranked boustrophedon, odd pairs backwards), dense raster width,
+    router beside / in front of the shared expert; unknown keys are refused."""
+    from sparse_b200 import ops, _lib
+    from sparse_b200.layer import LayerRunner, LayerWeights
+    lib = _lib.lib
+    torch.manual_seed(77)
+    bf = torch.bfloat16
+    h, i, e = 256, 192, 8
+    counts = [300, 1, 0, 129, 17, 520, 2, 64]
+    gate = [(torch.randn(i, h) * 0.05).to(bf) for _ in range(e)]
+    up = [(torch.randn(i, h) * 0.05).to(bf) for _ in range(e)]
+    down = [(torch.randn(h, i) * 0.05).to(bf) for _ in range(e)]
+    ids = torch.cat([torch.full((c,), ee, dtype=torch.int32) for ee, c in enumerate(counts)])
+    x = torch.randn(ids.numel(), h).to(bf)
+    p = ops.permute(x.to(dev()), ids.to(dev()), e, 1)
+    w13 = torch.stack([pack_w13(gate[ee], up[ee]) for ee in range(e)]).to(dev())
+    w2 = torch.stack(down).to(dev())
+    xd = torch.randn(700, h).to(bf).to(dev())
+    shape = synth.TINY
+    w = block_weights("TINY", 1.2)
+    runner = LayerRunner(LayerWeights.from_block_weights(w, dev()), shape.top_k, 300)
+    xl = synth.make_hidden(300, shape.hidden, seed=12).to(bf).to(dev())
+    try:
+        base = ops.grouped_swiglu(p.rows, w13, w2, tile_table=p.tile_table)[0].clone()
+        base_dense = ops.grouped_swiglu(xd, w13[:1], w2[:1], dense_rows=700)[0].clone()
+        base_layer = runner.forward(xl)[0].clone()
+        for key, values in ((b"sched", (1, 2, 0)), (b"dense_group", (2, 5, 1)), (b"router_overlap", (0, 1))):
+            for v in values:
+                assert lib.sb_set_tuning(key, v) == 0
+                assert torch.equal(ops.grouped_swiglu(p.rows, w13, w2, tile_table=p.tile_table)[0], base), (key, v)
+                assert torch.equal(ops.grouped_swiglu(xd, w13[:1], w2[:1], dense_rows=700)[0], base_dense), (key, v)
+                assert torch.equal(runner.forward(xl)[0], base_layer), (key, v)
+        assert lib.sb_set_tuning(b"sched", 3) != 0 and lib.sb_set_tuning(b"no_such_knob", 1) != 0
+        assert b"no_such_knob" in lib.sb_last_error_string()
+    finally:
+        lib.sb_set_tuning(b"sched", 0)
+        lib.sb_set_tuning(b"dense_group", 1)
+        lib.sb_set_tuning(b"router_overlap", 1)
+    runner.check_status()
+
+
 @pytest.mark.parametrize("bound", [0, 64])
 def test_mixed_swiglu_few_rows_per_expert(bound):
     """sb_grouped_swiglu_mixed (weight-streaming kernels, groups swept 16 rows at a
