@@ -74,6 +74,9 @@ int32_t sb_init(int32_t device);
  *                        1 with odd CTA pairs walking their list backwards
  *   "dense_group"    row chunks per raster block of a dense (shared-expert)
  *                    pass, 1..64 (default 1)
+ *   "kslabs"         K steps (64 deep) of a full tile per pipeline stage where
+ *                    the caller leaves the depth open: 2 (default, half the
+ *                    barrier round trips) or 1
  *   "router_overlap" 1 = sb_moe_layer_forward runs the router beside the shared
  *                    expert's gate/up pass (default), 0 = in front of it
  * Unknown keys and out-of-range values are SB_E_INVALID_ARG.  No counterpart in
@@ -234,9 +237,10 @@ int32_t sb_decode_experts_to(const void *x, const int32_t *item_of_slot, int32_t
 /* sb_grouped_swiglu restricted to one of its two passes: `passes` 1 = gate/up +
  * SwiGLU into `hbuf`, 2 = down projection from `hbuf` into `out`, 3 = both.
  * Lets a caller put other work (a transfer on another stream) between the
- * passes of the shared expert.  `stages` is the depth of the kernel's
- * shared-memory pipeline, 2..6 (0 = the default 5): with at most 5 an SM keeps
- * enough shared memory and registers free for one CTA of sb_router_topk launched
+ * passes of the shared expert.  `stages` names the kernel's shared-memory
+ * pipeline: 0 = the library's choice (three 64 KB stages of two K steps each),
+ * 2..6 = that many 36 KB stages of one K step, -1 = whichever layout leaves an
+ * SM enough shared memory and registers for one CTA of sb_router_topk launched
  * on another stream, which is how the router is hidden behind the shared
  * expert's gate/up pass. */
 int32_t sb_grouped_swiglu_passes(const void *rows, const int32_t *tile_table, int32_t dense_rows,

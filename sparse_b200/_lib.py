@@ -118,6 +118,20 @@ if lib.sb_moe_layer_struct_bytes() != C.sizeof(MoeLayer):
     raise ImportError("sparse_b200: struct sb_moe_layer of the library and its ctypes mirror differ")
 
 
+def apply_tuning_from_env(var: str = "SPARSE_B200_TUNING") -> None:
+    """`key=value,key=value` from the environment -> `sb_set_tuning` (the reference's
+    knobs are environment variables read by the block, utils/eval_core.py:4939-4968;
+    these only change scheduling, never results).  A bad entry raises."""
+    for item in filter(None, (t.strip() for t in os.environ.get(var, "").split(","))):
+        key, _, value = item.partition("=")
+        status = lib.sb_set_tuning(key.strip().encode(), int(value))
+        if status != SB_OK:
+            msg = lib.sb_last_error_string()
+            raise ValueError(f"{var}: {item!r} refused: {msg.decode() if msg else status}")
+
+
+apply_tuning_from_env()
+
 _initialised = set()
 
 

@@ -88,9 +88,9 @@ static int shared_pairs() {
   return v;
 }
 
-// Pipeline depth of a GEMM launch that should leave room for a router CTA on
-// every SM (see grouped_swiglu_pair.cu).
-constexpr int kStagesBesideRouter = 5;
+// "Depth" of a GEMM launch that should leave room for a router CTA on every SM
+// (the launcher picks the stage layout, see grouped_swiglu_pair.cu).
+constexpr int kStagesBesideRouter = -1;
 
 int32_t launch_grouped_swiglu_any(const void *rows, const int32_t *tile_table, int dense_rows,
                                   const void *w13, const void *w2, const int32_t *slot_of_expert,

@@ -60,7 +60,6 @@ constexpr int kMaxN = 256;           // tokens per tile (MMA N), multiple of 16
 constexpr int kBlockK = 64;
 constexpr int kStages = 6;           // most the shared memory holds
 constexpr int kDefaultStages = 5;    // measured on B200: a sixth stage gains nothing (the operand fetch is bandwidth-, not latency-bound)
-constexpr int kUmmaK = 16;
 constexpr int kThreads = 320;         // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = kRowsPerCta * kBlockK * 2;      // 16 KB
@@ -69,13 +68,20 @@ constexpr uint32_t kLightTokBytes = 16 * kBlockK * 2;         // 2 KB: a 16-row 
 // light tile (at most 16 tokens per CTA), TWO K steps (A, A', then the two
 // 2 KB token boxes): half as many barrier round trips per weight byte, twice
 // the bytes in flight, which is what bounds a tile that is pure weight traffic.
-constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kLightTokBytes;
+constexpr uint32_t kStageBytes = 2 * kABytes + 2 * kLightTokBytes;   // one K step per stage (36 KB)
+constexpr uint32_t kSlabBytes = 2 * kABytes;                        // A + B of one K step of a full tile
+constexpr uint32_t kStageBytes2 = 2 * kSlabBytes;                   // two K steps per stage (64 KB)
+constexpr int kStages2 = 3;                                         // most of those the shared memory holds
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kScatterTileBytes = 16 * kRowsPerCta * 2;    // 16 tokens x this CTA's 128 output columns, bf16
 constexpr int kMaxSched = 768;          // row chunks that can be ranked (larger tables are walked in table order)
 constexpr uint32_t kTailBytes = 256 + 2 * kScatterTileBytes + kMaxSched * 2;   // barriers, scatter staging, chunk order
-__host__ __device__ constexpr uint32_t smem_bytes(int stages) { return (uint32_t)stages * kStageBytes + 1024 + kTailBytes; }
-static_assert(smem_bytes(kStages) <= 232448, "shared memory of a CTA");
+// `tail` = false: a launch that neither scatters rows nor ranks chunks needs only
+// the barriers behind its stages.
+__host__ __device__ constexpr uint32_t smem_bytes(int stages, uint32_t stage_bytes = kStageBytes, bool tail = true) {
+  return (uint32_t)stages * stage_bytes + 1024 + (tail ? kTailBytes : 256u);
+}
+static_assert(smem_bytes(kStages) <= 232448 && smem_bytes(kStages2, kStageBytes2) <= 232448, "shared memory of a CTA");
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kSlotSkip = -2;
 constexpr int kModeSwiglu = 0, kModeScale = 1;
@@ -122,8 +128,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+// The slow half of a bounded wait, kept out of line so that the single-thread
+// producer and MMA loops stay short: spin, watch the abort flag, give up after
+// kWaitLimitNs.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
   const unsigned long long t0 = gtime_ns();
   for (;;) {
 #pragma unroll 1
@@ -132,6 +140,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort_flag) return false;
     if (gtime_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
 }
 // Tile loads of a CTA pair: destination in this CTA, completion bytes counted on
 // the barrier at `bar_cluster_addr` (the leader CTA's).
@@ -158,12 +171,22 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
       ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
-__device__ __forceinline__ void tc_mma_pair_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                                 uint32_t idesc, uint32_t accumulate) {
+// The four 16-deep MMAs of one 64-deep K step.  Descriptor start addresses are in
+// 16-byte units, so the k-th MMA reads 32 bytes (2 units) further along the
+// 128-byte swizzle row.  `accumulate` == 0 makes the first one overwrite D.
+__device__ __forceinline__ void tc_mma_pair_bf16_x4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                    uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 a, b;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %3, t;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -257,19 +280,24 @@ struct Sched {
   }
 };
 
+// The gate/up instance is held to 96 registers per thread (the "two CTAs per SM"
+// of its launch bounds says only that): with 320 threads that leaves an SM the
+// 32 K registers a router CTA needs beside it.
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, MODE == kModeSwiglu ? 2 : 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x16,
                  const int32_t *__restrict__ tile_table, int dense_rows,
                  const int32_t *__restrict__ slot_of_expert, const __nv_bfloat16 *__restrict__ row_scale,
                  __nv_bfloat16 *__restrict__ out, int ld_out, int w_rows, int num_kb, int n_slots,
                  int32_t *__restrict__ status, int skip_rows_upto, int dense_chunk, int light_max,
-                 const unsigned long long *__restrict__ row_dst, int n_stages, int sched_mode, int dense_group) {
+                 const unsigned long long *__restrict__ row_dst, int n_stages, int sched_mode, int dense_group,
+                 uint32_t stage_bytes) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t stage_bytes_all = (uint32_t)n_stages * kStageBytes;
+  const uint32_t stage_bytes_all = (uint32_t)n_stages * stage_bytes;
+  const int slabs = stage_bytes == kStageBytes2 ? 2 : 1;            // K steps of a full tile per stage
   const uint32_t bar_full = smem_base + stage_bytes_all;            // kStages  (used in the leader CTA)
   const uint32_t bar_empty = bar_full + 8 * kStages;               // kStages  (both CTAs)
   const uint32_t bar_tfull = bar_empty + 8 * kStages;              // 2        (both CTAs)
@@ -352,6 +380,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      const uint32_t full_leader0 = map_to_cta(bar_full, 0);
       for (int j = 0; ok && j < sch.rounds; ++j) {
         int c, wt;
         if (!sch.tile(j, c, wt)) continue;
@@ -367,17 +396,36 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const CUtensorMap *tok_map = half <= 16 ? &tm_x16 : (half <= 64 ? &tm_x64 : &tm_x);
         const uint32_t tok_bytes = (half <= 16 ? 16u : (half <= 64 ? 64u : 128u)) * kBlockK * 2;
         const bool light = half <= light_max;
-        for (int kb = 0; kb < num_kb; kb += light ? 2 : 1) {
+        if (!light) {
+          // one K step per stage; the loop is kept short: a lone thread has nothing
+          // to hide its instruction latencies behind, and it must turn a stage round
+          // faster than the tensor cores consume one
+          const uint32_t tx = 2 * (kABytes + tok_bytes);
+          for (int kb = 0; kb < num_kb; kb += slabs) {
+            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t sa = smem_base + stage * stage_bytes;
+            const bool two = slabs == 2 && kb + 1 < num_kb;
+            if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, two ? 2 * tx : tx);
+            tma_pair_load_3d(sa, &tm_w, full_leader0 + 8 * stage, kb * kBlockK, wrow, ch.slot);
+            tma_pair_load_2d(sa + kABytes, tok_map, full_leader0 + 8 * stage, kb * kBlockK, tok0);
+            if (two) {
+              tma_pair_load_3d(sa + kSlabBytes, &tm_w, full_leader0 + 8 * stage, (kb + 1) * kBlockK, wrow, ch.slot);
+              tma_pair_load_2d(sa + kSlabBytes + kABytes, tok_map, full_leader0 + 8 * stage, (kb + 1) * kBlockK, tok0);
+            }
+            if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+          }
+          continue;
+        }
+        for (int kb = 0; kb < num_kb; kb += 2) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
-          const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
-          const uint32_t sa = smem_base + stage * kStageBytes;
-          const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
+          const uint32_t full_leader = full_leader0 + 8 * stage;
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const int steps = kb + 1 < num_kb ? 2 : 1;
           if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * steps * (kABytes + tok_bytes));
           for (int q = 0; q < steps; ++q)
             tma_pair_load_3d(sa + q * kABytes, &tm_w, full_leader, (kb + q) * kBlockK, wrow, ch.slot);
           for (int q = 0; q < steps; ++q)
-            tma_pair_load_2d(light ? sa + 2 * kABytes + q * kLightTokBytes : sa + kABytes, tok_map, full_leader,
-                             (kb + q) * kBlockK, tok0);
+            tma_pair_load_2d(sa + 2 * kABytes + q * kLightTokBytes, tok_map, full_leader, (kb + q) * kBlockK, tok0);
           if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -388,6 +436,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
+      const uint64_t desc_fixed = umma_desc_sw128(0);     // everything but the start address (shared memory is below 256 KB)
       for (int j = 0; ok && j < sch.rounds; ++j) {
         int c, wt;
         if (!sch.tile(j, c, wt)) continue;
@@ -399,21 +448,31 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * kMaxN;
         const bool light = (n >> 1) <= light_max;
-        for (int kb = 0; kb < num_kb; kb += light ? 2 : 1) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_base + stage * kStageBytes;
-          const int steps = (light && kb + 1 < num_kb) ? 2 : 1;
-          for (int q = 0; q < steps; ++q) {
-            const uint64_t adesc = umma_desc_sw128(sa + q * kABytes);
-            const uint64_t bdesc = umma_desc_sw128(light ? sa + 2 * kABytes + q * kLightTokBytes : sa + kABytes);
-#pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                               (kb | q | k) != 0 ? 1u : 0u);
+        if (!light) {
+          for (int kb = 0; kb < num_kb; kb += slabs) {
+            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t adesc = desc_fixed | (uint64_t)((smem_base + stage * stage_bytes) >> 4);
+            tc_mma_pair_bf16_x4(d_tmem, adesc, adesc + (kABytes >> 4), idesc, (uint32_t)kb);
+            if (slabs == 2 && kb + 1 < num_kb)
+              tc_mma_pair_bf16_x4(d_tmem, adesc + (kSlabBytes >> 4), adesc + ((kSlabBytes + kABytes) >> 4), idesc, 1u);
+            tc_commit_pair(bar_empty + 8 * stage);
+            if (++stage == n_stages) { stage = 0; phase ^= 1u; }
           }
-          tc_commit_pair(bar_empty + 8 * stage);
-          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+        } else {
+          for (int kb = 0; kb < num_kb; kb += 2) {
+            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_base + stage * stage_bytes;
+            const int steps = kb + 1 < num_kb ? 2 : 1;
+            for (int q = 0; q < steps; ++q) {
+              const uint64_t adesc = umma_desc_sw128(sa + q * kABytes);
+              const uint64_t bdesc = umma_desc_sw128(sa + 2 * kABytes + q * kLightTokBytes);
+              tc_mma_pair_bf16_x4(d_tmem, adesc, bdesc, idesc, (uint32_t)(kb | q));
+            }
+            tc_commit_pair(bar_empty + 8 * stage);
+            if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+          }
         }
         if (!ok) break;
         tc_commit_pair(bar_tfull + 8 * acc);
@@ -466,7 +525,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           // The even lane (gate row) finishes the even tokens of the chunk, the odd
           // lane (up row) the odd ones: each sends the partner the value it will
           // not use itself.  One shuffle per token pair, no divergent branch.
-          __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0 + (odd ? 1 : 0)) * ld_out + feat;
+          // all the arithmetic first, in one straight run of independent chains,
+          // then the guarded stores: a branch per element would serialise the chains
+          __nv_bfloat16 hv[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float keep = round_bf16(__uint_as_float(odd ? v[2 * i + 1] : v[2 * i]));
@@ -474,9 +535,13 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             const float got = __shfl_xor_sync(0xffffffffu, give, 1);
             const float g = odd ? got : keep, u = odd ? keep : got;
             const float s = round_bf16(__fdividef(g, 1.0f + __expf(-g)));
-            const __nv_bfloat16 h = __float2bfloat16_rn(s * u);
-            if (feat_ok && c0 + 2 * i + (odd ? 1 : 0) < n_tok) obase[(size_t)(2 * i) * ld_out] = h;
+            hv[i] = __float2bfloat16_rn(s * u);
           }
+          __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0 + (odd ? 1 : 0)) * ld_out + feat;
+          const int left = feat_ok ? n_tok - c0 - (odd ? 1 : 0) : 0;     // tokens 2i < left are this lane's to write
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (2 * i < left) obase[(size_t)(2 * i) * ld_out] = hv[i];
         }
       } else {
         const bool col_ok = wrow < ld_out;
@@ -490,13 +555,17 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (row_scale != nullptr && c0 + lane < n_tok)
             my_scale = __bfloat162float(row_scale[ch.tok_begin + c0 + lane]);
           if (row_dst == nullptr) {
-            __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
+            __nv_bfloat16 yv[32];
 #pragma unroll
             for (int q = 0; q < 32; ++q) {
               const float sc = __shfl_sync(0xffffffffu, my_scale, q);
-              const float y = round_bf16(__uint_as_float(v[q])) * sc;
-              if (col_ok && c0 + q < n_tok) obase[(size_t)q * ld_out] = __float2bfloat16_rn(y);
+              yv[q] = __float2bfloat16_rn(round_bf16(__uint_as_float(v[q])) * sc);
             }
+            __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
+            const int left = col_ok ? n_tok - c0 : 0;
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (q < left) obase[(size_t)q * ld_out] = yv[q];
           } else {
             // Scatter: every row goes straight to the address its sender asked for
             // (a row of the sender's return buffer, possibly on another GPU), so
@@ -557,6 +626,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
 // Tuning knobs behind sb_set_tuning (process-wide, read at launch time).
 std::atomic<int> g_sched_mode{0};      // 0 table order / fixed stride, 1 ranked boustrophedon, 2 odd pairs backwards
+std::atomic<int> g_kslabs{2};          // K steps of a full tile per pipeline stage when the caller leaves the depth open
 std::atomic<int> g_dense_group{1};     // dense passes: row chunks per raster block (1 = chunk-major walk)
 int sched_mode() { return g_sched_mode.load(std::memory_order_relaxed); }
 
@@ -675,18 +745,20 @@ template <int MODE>
 int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int32_t *tile_table, int dense_rows,
                     const int32_t *slot_of_expert, const void *row_scale, void *out, int ld_out, int w_rows,
                     int num_kb, int n_slots, int32_t *status, int grid, int skip_rows_upto,
-                    const unsigned long long *row_dst, int n_stages, cudaStream_t stream) {
+                    const unsigned long long *row_dst, int n_stages, uint32_t stage_bytes, cudaStream_t stream) {
   const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
   const int dense_chunk = tile_table == nullptr ? dense_chunk_rows(dense_rows, n_wtiles, grid / 2) : kMaxN;
   const int probe_light = 16;
   auto kern = pair_gemm_kernel<MODE>;
-  kern<<<grid, kThreads, smem_bytes(n_stages), stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
+  const int mode_now = sched_mode();
+  const bool tail = row_dst != nullptr || (tile_table != nullptr && mode_now != 0);
+  kern<<<grid, kThreads, smem_bytes(n_stages, stage_bytes, tail), stream>>>(tm_w, tm_x[0], tm_x[1], tm_x[2], tile_table, dense_rows,
                                                         slot_of_expert,
                                                         static_cast<const __nv_bfloat16 *>(row_scale),
                                                         static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb,
                                                         n_slots, status, skip_rows_upto, dense_chunk, probe_light,
-                                                        row_dst, n_stages, sched_mode(),
-                                                        g_dense_group.load(std::memory_order_relaxed));
+                                                        row_dst, n_stages, mode_now,
+                                                        g_dense_group.load(std::memory_order_relaxed), stage_bytes);
   SB_LAUNCH_CHECK();
   return SB_OK;
 }
@@ -702,6 +774,11 @@ int32_t set_gemm_tuning(const char *key, int value) {
   if (strcmp(key, "dense_group") == 0) {
     if (value < 1 || value > 64) return fail(SB_E_INVALID_ARG, "sb_set_tuning: dense_group must be in [1,64]");
     g_dense_group.store(value);
+    return SB_OK;
+  }
+  if (strcmp(key, "kslabs") == 0) {
+    if (value != 1 && value != 2) return fail(SB_E_INVALID_ARG, "sb_set_tuning: kslabs must be 1 or 2");
+    g_kslabs.store(value);
     return SB_OK;
   }
   return SB_E_UNSUPPORTED;      // not a GEMM key
@@ -729,7 +806,18 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (!rows || !w13 || !w2 || !hbuf || (!out && !row_dst)) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: null pointer");
   if (!aligned(rows, 128) || !aligned(w13, 128) || !aligned(w2, 128) || !aligned(hbuf, 128) || (out && !aligned(out, 16)))
     return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: operands must be 128-byte aligned");
-  if (stages == 0) stages = kDefaultStages;
+  // Depth left open: three 64 KB stages of two K steps each (half the barrier
+  // round trips per K step).  A caller that names a depth gets 36 KB stages of
+  // one K step, e.g. five of them to leave room on the SM for a router CTA.
+  uint32_t stage_bytes = kStageBytes;
+  // -1: the launch should leave room on every SM for one router CTA.  Three
+  // 64 KB stages without the scatter/ranking tail do (193 KB + the router's
+  // 30 KB); with one K step per stage it is five 36 KB stages.
+  if (stages == -1) stages = g_kslabs.load(std::memory_order_relaxed) == 2 ? 0 : kDefaultStages;
+  if (stages == 0) {
+    if (g_kslabs.load(std::memory_order_relaxed) == 2) { stages = kStages2; stage_bytes = kStageBytes2; }
+    else stages = kDefaultStages;
+  }
   if (stages < 2 || stages > kStages) return fail(SB_E_INVALID_ARG, "sb_grouped_swiglu: stages=%d outside [2,%d]", stages, kStages);
   int32_t rc = prepare_device();
   if (rc != SB_OK) return rc;
@@ -746,12 +834,12 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
   if (max_pairs > 0 && 2 * max_pairs < grid) grid = 2 * max_pairs;     // leave the other SMs to a concurrent launch
   if (passes & 1) {
     rc = launch_pass<kModeSwiglu>(tm_w13, tm_x, tile_table, dense_rows, slot_of_expert, nullptr, hbuf, I, 2 * I,
-                                  H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stages, stream);
+                                  H / kBlockK, S, status, grid, skip_rows_upto, nullptr, stages, stage_bytes, stream);
     if (rc != SB_OK) return rc;
   }
   if (!(passes & 2)) return SB_OK;
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
-                                 I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stages, stream);
+                                 I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stages, stage_bytes, stream);
 }
 
 }  // namespace sb

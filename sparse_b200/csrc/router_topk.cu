@@ -403,10 +403,10 @@ template <typename IN, int TB>
 int32_t launch_router_tb(const void *x, const void *wg, const float *bias, const void *wsg, int T,
                          int H, int E, int K, int renorm, int fp32_logits, int32_t *out_idx,
                          void *out_w, void *out_logits, void *out_shared, cudaStream_t stream) {
-  size_t smem = (size_t)TB * H * sizeof(IN) + (size_t)TB * (E + 1) * sizeof(float);
+  const size_t smem_max = (size_t)TB * H * sizeof(IN) + (size_t)TB * (E + 1) * sizeof(float);
   auto kern = router_kernel<IN, TB>;
-  if (smem > 48 * 1024)
-    SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (smem_max > 48 * 1024)
+    SB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
   // tokens per CTA: as few as keeps the grid within four CTAs per SM, so the
   // last wave is full (4096 tokens on 148 SMs -> 7 per CTA, 586 CTAs)
   const int slots = 4 * (sb_device_sm_count() > 0 ? sb_device_sm_count() : 148);
@@ -414,7 +414,7 @@ int32_t launch_router_tb(const void *x, const void *wg, const float *bias, const
   if (tb_eff < 1) tb_eff = 1;
   if (tb_eff > TB) tb_eff = TB;
   int blocks = (T + tb_eff - 1) / tb_eff;
-  kern<<<blocks, kRouterThreads, smem, stream>>>(
+  kern<<<blocks, kRouterThreads, smem_max, stream>>>(
       static_cast<const IN *>(x), static_cast<const IN *>(wg), bias, static_cast<const IN *>(wsg),
       T, H, E, K, renorm, fp32_logits, tb_eff, out_idx, static_cast<IN *>(out_w), out_logits,
       static_cast<IN *>(out_shared));
@@ -429,6 +429,13 @@ int32_t launch_router_t(const void *x, const void *wg, const float *bias, const 
   // Fewer tokens per CTA when there are few tokens, so decode-sized calls still
   // spread over the SMs; 16 per CTA at prefill sizes to amortise the weight reads.
   const size_t tile8 = (size_t)8 * H * sizeof(IN) + 8 * (size_t)(E + 1) * 4;
+  // 7 when that is all a CTA takes anyway (4096 tokens over four CTAs per SM on
+  // 148 SMs): the tile is sized by the template, and the less shared memory a
+  // router CTA asks for, the more of the SM a GEMM CTA of another stream keeps
+  const int sms = sb_device_sm_count() > 0 ? sb_device_sm_count() : 148;
+  if (T >= 1024 && tile8 <= 100 * 1024 && (T + 4 * sms - 1) / (4 * sms) <= 7)
+    return launch_router_tb<IN, 7>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
+                                    out_w, out_logits, out_shared, stream);
   if (T >= 1024 && tile8 <= 100 * 1024)
     return launch_router_tb<IN, 8>(x, wg, bias, wsg, T, H, E, K, renorm, fp32_logits, out_idx,
                                     out_w, out_logits, out_shared, stream);

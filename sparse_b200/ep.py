@@ -372,7 +372,7 @@ class EpRank:
     def stage_shared(self, passes: int = 3, stages: int = 0) -> None:
         """The shared expert on this rank's own tokens; `passes` 1 / 2 run only its
         gate/up or only its down pass (batches above the decode size), `stages`
-        is the GEMM's pipeline depth (5 leaves room for a router CTA on each SM)."""
+        names the GEMM pipeline (-1 leaves room for a router CTA on each SM)."""
         w, t = self.w, self._t
         if not w.shared_inter or t == 0:
             return
@@ -584,7 +584,7 @@ class ExpertParallelLayer:
                 stamp("begin", stream)
                 self._fork.record(stream)
                 if has_shared:
-                    r.stage_shared(1, stages=5)
+                    r.stage_shared(1, stages=-1)
                     stamp("main: shared gate/up done", stream)
                 with torch.cuda.stream(self._side):
                     self._side.wait_event(self._fork)

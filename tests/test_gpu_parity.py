@@ -270,7 +270,8 @@ def test_grouped_swiglu_against_oracle(h, i, e, counts):
 def test_tuning_knobs_change_the_schedule_not_the_bits():
     """Every setting of sb_set_tuning gives bit-identical rows: tile walk (table
     order, ranked boustrophedon, odd pairs backwards), dense raster width,
-    router beside / in front of the shared expert; unknown keys are refused."""
+    router beside / in front of the shared expert, one or two K steps per
+    pipeline stage; unknown keys are refused."""
     from sparse_b200 import ops, _lib
     from sparse_b200.layer import LayerRunner, LayerWeights
     lib = _lib.lib
@@ -296,7 +297,8 @@ def test_tuning_knobs_change_the_schedule_not_the_bits():
         base = ops.grouped_swiglu(p.rows, w13, w2, tile_table=p.tile_table)[0][:n].clone()
         base_dense = ops.grouped_swiglu(xd, w13[:1], w2[:1], dense_rows=700)[0].clone()
         base_layer = runner.forward(xl)[0].clone()
-        for key, values in ((b"sched", (1, 2, 0)), (b"dense_group", (2, 5, 1)), (b"router_overlap", (0, 1))):
+        for key, values in ((b"sched", (1, 2, 0)), (b"dense_group", (2, 5, 1)), (b"router_overlap", (0, 1)),
+                            (b"kslabs", (1, 2))):
             for v in values:
                 assert lib.sb_set_tuning(key, v) == 0
                 assert torch.equal(ops.grouped_swiglu(p.rows, w13, w2, tile_table=p.tile_table)[0][:n], base), (key, v)
@@ -308,6 +310,7 @@ def test_tuning_knobs_change_the_schedule_not_the_bits():
         lib.sb_set_tuning(b"sched", 0)
         lib.sb_set_tuning(b"dense_group", 1)
         lib.sb_set_tuning(b"router_overlap", 1)
+        lib.sb_set_tuning(b"kslabs", 2)
     runner.check_status()
 
 
