@@ -336,6 +336,16 @@ int32_t sb_combine(const void *rows_out, const int32_t *slot_of_item,
                    const int32_t *idx, const void *shared_out, int32_t T, int32_t H,
                    int32_t K, void *out, void *stream);
 
+/* sb_combine that also applies the shared expert's scalar gate: the row added is
+ * bf16(shared_out[t] * shared_scale[t]) (`shared_scale` [T] bf16 as written by
+ * sb_router_topk, NULL = as sb_combine).  Same bits as letting the shared
+ * expert's down pass scale its rows (row_scale of sb_grouped_swiglu), but that
+ * pass then needs nothing from the router
+ * (utils/eval_core.py:9455-9463: gate multiply, then the add). */
+int32_t sb_combine_gated(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
+                         const void *shared_out, const void *shared_scale, int32_t T, int32_t H, int32_t K,
+                         void *out, void *stream);
+
 /*
  * Asynchronous copy of one expert payload into a preallocated cache slot on
  * `stream` (pinned host memory, a peer GPU, or this GPU).  Callable from a

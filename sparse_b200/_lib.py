@@ -65,6 +65,7 @@ SIGNATURES: Dict[str, Tuple[object, list]] = {
     "sb_route_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                               vp, vp]),
     "sb_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
+    "sb_combine_gated": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "sb_slot_copy_async": (i32, [vp, vp, sz, i32, i32, vp]),
     "sb_peer_alloc": (i32, [sz, C.POINTER(vp)]),
     "sb_peer_free": (i32, [vp]),

@@ -84,7 +84,10 @@ __host__ __device__ constexpr uint32_t smem_bytes(int stages, uint32_t stage_byt
 static_assert(smem_bytes(kStages) <= 232448 && smem_bytes(kStages2, kStageBytes2) <= 232448, "shared memory of a CTA");
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kSlotSkip = -2;
-constexpr int kModeSwiglu = 0, kModeScale = 1;
+// kModePlain: the down pass of a launch without route weights and without row
+// destinations (the shared expert's): bf16 rounding and plain stores only, held
+// to 96 registers like the gate/up instance so that a router CTA fits beside it.
+constexpr int kModeSwiglu = 0, kModeScale = 1, kModePlain = 2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -284,7 +287,7 @@ struct Sched {
 // of its launch bounds says only that): with 320 threads that leaves an SM the
 // 32 K registers a router CTA needs beside it.
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, MODE == kModeSwiglu ? 2 : 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, MODE == kModeScale ? 1 : 2)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x16,
                  const int32_t *__restrict__ tile_table, int dense_rows,
@@ -550,22 +553,35 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           uint32_t v[32];
           tc_ld32(taddr + c0, v);
           tc_wait_ld();
-          // this lane's route weight of token c0+lane; handed round by shuffle
-          float my_scale = 1.0f;
-          if (row_scale != nullptr && c0 + lane < n_tok)
-            my_scale = __bfloat162float(row_scale[ch.tok_begin + c0 + lane]);
-          if (row_dst == nullptr) {
-            __nv_bfloat16 yv[32];
+          // This lane's route weight of token c0+lane, packed with its right
+          // neighbour's: pair k = (weights of tokens 2k, 2k+1), handed round by one
+          // shuffle per pair.  The product of two bf16 values is exact in fp32, so
+          // the packed bf16 multiply (one rounding) gives the bits of the fp32
+          // multiply followed by the rounding to bf16.
+          __nv_bfloat16 my_scale_b = __float2bfloat16_rn(1.0f);
+          if (MODE != kModePlain && row_scale != nullptr && c0 + lane < n_tok)
+            my_scale_b = row_scale[ch.tok_begin + c0 + lane];
+          const uint32_t my_bits = (uint32_t)__bfloat16_as_ushort(my_scale_b);
+          const uint32_t scale_pair = my_bits | (__shfl_down_sync(0xffffffffu, my_bits, 1) << 16);
+          if (MODE == kModePlain || row_dst == nullptr) {
+            uint32_t yv[16];
 #pragma unroll
-            for (int q = 0; q < 32; ++q) {
-              const float sc = __shfl_sync(0xffffffffu, my_scale, q);
-              yv[q] = __float2bfloat16_rn(round_bf16(__uint_as_float(v[q])) * sc);
+            for (int k = 0; k < 16; ++k) {
+              const __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+              __nv_bfloat162 y = a;
+              if (MODE != kModePlain) {
+                const uint32_t sp = __shfl_sync(0xffffffffu, scale_pair, 2 * k);
+                y = __hmul2(a, *reinterpret_cast<const __nv_bfloat162 *>(&sp));
+              }
+              yv[k] = *reinterpret_cast<const uint32_t *>(&y);
             }
-            __nv_bfloat16 *obase = out + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
+            unsigned short *obase = reinterpret_cast<unsigned short *>(out) + (size_t)(ch.tok_begin + c0) * ld_out + wrow;
             const int left = col_ok ? n_tok - c0 : 0;
 #pragma unroll
-            for (int q = 0; q < 32; ++q)
-              if (q < left) obase[(size_t)q * ld_out] = yv[q];
+            for (int k = 0; k < 16; ++k) {
+              if (2 * k < left) obase[(size_t)(2 * k) * ld_out] = (unsigned short)(yv[k] & 0xffffu);
+              if (2 * k + 1 < left) obase[(size_t)(2 * k + 1) * ld_out] = (unsigned short)(yv[k] >> 16);
+            }
           } else {
             // Scatter: every row goes straight to the address its sender asked for
             // (a row of the sender's return buffer, possibly on another GPU), so
@@ -580,10 +596,13 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
-              for (int q = 0; q < 16; ++q) {
-                const float sc = __shfl_sync(0xffffffffu, my_scale, sub * 16 + q);
-                const float y = round_bf16(__uint_as_float(v[sub * 16 + q])) * sc;
-                stg[q * kRowsPerCta + wl] = __float2bfloat16_rn(y);
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t sp = __shfl_sync(0xffffffffu, scale_pair, sub * 16 + 2 * k);
+                const __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(v[sub * 16 + 2 * k]),
+                                                               __uint_as_float(v[sub * 16 + 2 * k + 1]));
+                const __nv_bfloat162 y = __hmul2(a, *reinterpret_cast<const __nv_bfloat162 *>(&sp));
+                stg[(2 * k) * kRowsPerCta + wl] = y.x;
+                stg[(2 * k + 1) * kRowsPerCta + wl] = y.y;
               }
               asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
 #pragma unroll
@@ -711,11 +730,15 @@ int32_t prepare_device() {
                                      (int)smem_bytes(kStages)));
   SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeScale>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem_bytes(kStages)));
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModePlain>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes(kStages)));
   // the largest shared-memory split, so that small kernels of other streams
   // (router, sort, gather) can share an SM with a resident GEMM CTA
   SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeSwiglu>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      (int)cudaSharedmemCarveoutMaxShared));
   SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModeScale>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
+  SB_CUDA_CHECK(cudaFuncSetAttribute(pair_gemm_kernel<kModePlain>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      (int)cudaSharedmemCarveoutMaxShared));
   done[dev] = true;
   return SB_OK;
@@ -838,6 +861,9 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
     if (rc != SB_OK) return rc;
   }
   if (!(passes & 2)) return SB_OK;
+  if (row_scale == nullptr && row_dst == nullptr)
+    return launch_pass<kModePlain>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, nullptr, out, H, H,
+                                   I / kBlockK, S, status, grid, skip_rows_upto, nullptr, stages, stage_bytes, stream);
   return launch_pass<kModeScale>(tm_w2, tm_h, tile_table, dense_rows, slot_of_expert, row_scale, out, H, H,
                                  I / kBlockK, S, status, grid, skip_rows_upto, row_dst, stages, stage_bytes, stream);
 }

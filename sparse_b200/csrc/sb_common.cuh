@@ -116,6 +116,6 @@ int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int it
                               int32_t *status, int ctas_per_sm, int max_rows, const void *shared_x,
                               const unsigned long long *row_dst, cudaStream_t stream);
 int32_t launch_combine(const void *rows_out, const int32_t *slot_of_item, const int32_t *idx,
-                       const void *shared_out, int T, int H, int K, void *out,
+                       const void *shared_out, const void *shared_scale, int T, int H, int K, void *out,
                        cudaStream_t stream);
 }  // namespace sb

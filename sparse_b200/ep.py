@@ -251,7 +251,10 @@ class EpRank:
             raise RuntimeError("EP layer was sized for %d tokens, got %d" % (self.max_tokens, x.shape[0]))
         self._x, self._t = x, x.shape[0]
 
-    def stage_route(self, x: Optional[torch.Tensor] = None) -> None:
+    def stage_route(self, x: Optional[torch.Tensor] = None, part: str = "both") -> None:
+        """Router and local expert sort; above the decode size `part` = "router" /
+        "sort" runs only that launch group (the sort is one CTA and can sit beside
+        a GEMM, the router wants the machine)."""
         if x is not None:
             self.begin(x)
         w, x, t, k = self.w, self._x, self._t, self.top_k
@@ -268,20 +271,23 @@ class EpRank:
                 self.local_scale.data_ptr(), self.local_tiles.data_ptr(), self._s()), "sb_route_decode")
             self.launches += 2
             return
-        check(lib.sb_router_topk(
-            x.data_ptr(), w.router_w.data_ptr(),
-            w.router_bias.data_ptr() if w.router_bias is not None else None,
-            w.shared_gate_w.data_ptr() if w.shared_gate_w is not None else None,
-            t, w.hidden, w.num_experts, k, int(self.renorm), _lib.SB_DTYPE_BF16, int(self.fp32_logits),
-            self.topk_idx.data_ptr(), self.topk_w.data_ptr(), self.logits.data_ptr(),
-            self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, self._s()),
-            "sb_router_topk")
-        check(lib.sb_permute(
-            None, self.topk_idx.data_ptr(), None, t * k, k, w.hidden, w.num_experts,
-            self.sort_ws.data_ptr(), self.sort_ws.numel(), None, self.local_offsets.data_ptr(),
-            self.slot_of_item.data_ptr(), self.item_of_slot.data_ptr(), None,
-            self.local_tiles.data_ptr(), self._s()), "sb_permute")
-        self.launches += 4
+        if part in ("both", "router"):
+            check(lib.sb_router_topk(
+                x.data_ptr(), w.router_w.data_ptr(),
+                w.router_bias.data_ptr() if w.router_bias is not None else None,
+                w.shared_gate_w.data_ptr() if w.shared_gate_w is not None else None,
+                t, w.hidden, w.num_experts, k, int(self.renorm), _lib.SB_DTYPE_BF16, int(self.fp32_logits),
+                self.topk_idx.data_ptr(), self.topk_w.data_ptr(), self.logits.data_ptr(),
+                self.shared_scale.data_ptr() if w.shared_gate_w is not None else None, self._s()),
+                "sb_router_topk")
+            self.launches += 1
+        if part in ("both", "sort"):
+            check(lib.sb_permute(
+                None, self.topk_idx.data_ptr(), None, t * k, k, w.hidden, w.num_experts,
+                self.sort_ws.data_ptr(), self.sort_ws.numel(), None, self.local_offsets.data_ptr(),
+                self.slot_of_item.data_ptr(), self.item_of_slot.data_ptr(), None,
+                self.local_tiles.data_ptr(), self._s()), "sb_permute")
+            self.launches += 3
 
     def stage_publish(self) -> None:
         check(lib.sb_ep_publish_counts(self.local_offsets.data_ptr(), self.w.num_experts, self.rank,
@@ -495,6 +501,7 @@ class ExpertParallelLayer:
                         owner_decode=owner_decode)
         self.last_launches = 0
         self.overlap = True
+        self.router_first = os.environ.get("SPARSE_B200_EP_ROUTER_FIRST", "1") != "0"
         with torch.cuda.device(weights.device):
             self._side = torch.cuda.Stream(device=weights.device)
             self._fork = torch.cuda.Event()
@@ -564,13 +571,16 @@ class ExpertParallelLayer:
                 self.last_launches = r.launches
                 return res
             else:
-                # The shared expert's gate/up pass needs nothing from the routing
-                # and its down pass only the scalar gate, so the whole send side
-                # runs beside it on the side stream: router, sort, counts, plan,
-                # dispatch and the "rows landed" barrier.  The gate/up launch goes
-                # first with a pipeline one stage short, which leaves each SM room
-                # for one router CTA: the router's CUDA-core dot products run under
-                # the tensor-core pass, not in front of it.
+                # The router and the sort run first, alone: beside a GEMM a router
+                # CTA gets one slot per SM and a share of the issue cycles, takes
+                # 190 us instead of 73 us, and everything that follows it (counts,
+                # plan, dispatch, the barriers, and the shared expert's down pass,
+                # which needs the scalar gate) starts that much later.  Then the
+                # send side (counts, plan, dispatch, "rows landed" barrier) runs on
+                # the side stream beside both passes of the shared expert.
+                # `router_first = False` gives the other order: router beside the
+                # shared gate/up pass (what the single-GPU layer does, where there
+                # is no send side to wait for).
                 tl = self.timeline
 
                 def stamp(name, st):
@@ -582,15 +592,22 @@ class ExpertParallelLayer:
                 r.begin(x)
                 has_shared = bool(r.w.shared_inter)
                 stamp("begin", stream)
+                if self.router_first:
+                    r.stage_route(part="router")
+                    stamp("main: router done", stream)
                 self._fork.record(stream)
-                if has_shared:
+                if has_shared and not self.router_first:
                     r.stage_shared(1, stages=-1)
                     stamp("main: shared gate/up done", stream)
                 with torch.cuda.stream(self._side):
                     self._side.wait_event(self._fork)
-                    r.stage_route()
-                    stamp("side: router+sort done", self._side)
-                    self._mid.record(self._side)
+                    if self.router_first:
+                        r.stage_route(part="sort")
+                        stamp("side: sort done", self._side)
+                    else:
+                        r.stage_route()
+                        stamp("side: router+sort done", self._side)
+                        self._mid.record(self._side)
                     r.stage_publish()
                     self._barrier()
                     stamp("side: counts exchanged", self._side)
@@ -601,7 +618,11 @@ class ExpertParallelLayer:
                     r.stage_resolve()
                     stamp("side: rows landed", self._side)
                     self._join.record(self._side)
-                stream.wait_event(self._mid)            # the scalar gate of the shared expert is known
+                if has_shared and self.router_first:
+                    r.stage_shared(1)
+                    stamp("main: shared gate/up done", stream)
+                if not self.router_first:
+                    stream.wait_event(self._mid)        # the scalar gate of the shared expert is known
                 if has_shared:
                     r.stage_shared(2)
                     stamp("main: shared down done", stream)
