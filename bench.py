@@ -44,11 +44,11 @@ N_INPUT_BATCHES = 4          # rotated so a step never re-reads the previous ste
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel
 # (pair_gemm_kernel), averaged over the four launches of one step (routed
-# gate/up 739.6 MB, routed down 412.6 MB, shared gate/up 102.4 MB, shared down
-# 74.2 MB = 1328.8 MB per step), from one `ncu --set full` capture of this
+# gate/up 737.1 MB, routed down 412.4 MB, shared gate/up 105.7 MB, shared down
+# 74.9 MB = 1330.1 MB per step), from one `ncu --set full` capture of this
 # workload on a B200 (2026-11-25).  The algorithmic bytes of the same four
 # launches are 1355.8 MB: nothing is re-read from DRAM.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 332198848
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 332530368
 
 
 def _peaks():

@@ -745,21 +745,17 @@ int32_t prepare_device() {
 }
 
 // Rows per chunk of a dense (single-slot) pass: the multiple of 16 in [192, 256]
-// that gives the cheapest schedule over `pairs` CTA pairs, a tile of c rows
-// costing c + 256 (its MMA time grows with c, the weight tile it streams does
-// not).  4096 rows x 8 weight tiles on 74 pairs: chunks of 256 make 128 tiles =
-// two rounds of 256-row tiles; chunks of 240 make 144 tiles = two rounds of
-// 240-row tiles.
+// that needs the fewest rounds over `pairs` CTA pairs; among equals the widest.
+// A tile's MMA time does not depend on its token extent (measured on B200: the
+// same with 64, 128 or 256 tokens), so a round costs the same whatever the chunk
+// width and only the number of rounds counts.
 int dense_chunk_rows(int rows, int n_wtiles, int pairs) {
   int best = kMaxN;
-  long best_cost = -1;
+  long best_rounds = -1;
   for (int c = kMaxN; c >= 192; c -= 16) {
-    const long full = rows / c, rest = rows - full * c;
-    const long rounds_full = (full * n_wtiles + pairs - 1) / pairs;
-    // the remainder chunk's tiles ride along in the last round if it has room, else they add a short round
-    const long spare = rounds_full * pairs - full * n_wtiles;
-    const long cost = rounds_full * (c + 256) + ((rest > 0 && spare < n_wtiles) ? (((rest + 15) & ~15L) + 256) : 0);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = c; }
+    const long chunks = (rows + c - 1) / c;
+    const long rounds = (chunks * n_wtiles + pairs - 1) / pairs;
+    if (best_rounds < 0 || rounds < best_rounds) { best_rounds = rounds; best = c; }
   }
   return best;
 }
