@@ -653,7 +653,9 @@ def cache_stress(args):
                 y = lay[l].forward(x)
                 if record is not None:
                     row.append(lay[l]._idx_host[0].tolist())     # already on the host
-                x = x + y
+                # residual add + RMS norm, as the model does between its MoE blocks: without
+                # the norm the hidden state of a 24-layer stack overflows bf16
+                x = torch.nn.functional.rms_norm((x + y).float(), (shape.hidden,)).to(torch.bfloat16)
             if record is not None:
                 record.append(row)
             outs = x

@@ -77,6 +77,9 @@ int32_t sb_init(int32_t device);
  *   "kslabs"         K steps (64 deep) of a full tile per pipeline stage where
  *                    the caller leaves the depth open: 2 (default, half the
  *                    barrier round trips) or 1
+ *   "dispatch_ctas"  CTAs per SM of sb_ep_dispatch, 1..8 (default 1: the kernel
+ *                    runs beside the shared expert's GEMM, and fewer resident
+ *                    warps leave that GEMM its issue slots)
  *   "router_overlap" 1 = sb_moe_layer_forward runs the router beside the shared
  *                    expert's gate/up pass (default), 0 = in front of it
  * Unknown keys and out-of-range values are SB_E_INVALID_ARG.  No counterpart in

@@ -254,6 +254,7 @@ int32_t sb_set_tuning(const char *key, int32_t value) {
     return SB_OK;
   }
   int32_t rc = set_gemm_tuning(key, value);
+  if (rc == SB_E_UNSUPPORTED) rc = set_ep_tuning(key, value);
   if (rc == SB_E_UNSUPPORTED) return fail(SB_E_INVALID_ARG, "sb_set_tuning: unknown key '%s'", key);
   return rc;
 }

@@ -34,9 +34,24 @@
 // barrier must never share one GPU.
 #include <string.h>
 
+#include <atomic>
+
 #include "sb_common.cuh"
 
 namespace sb {
+
+// CTAs of the dispatch kernel per SM (sb_set_tuning("dispatch_ctas", 1..8)).
+static std::atomic<int> g_dispatch_ctas{1};
+int32_t set_ep_tuning(const char *key, int value) {
+  if (strcmp(key, "dispatch_ctas") == 0) {
+    if (value < 1 || value > 8) return fail(SB_E_INVALID_ARG, "sb_set_tuning: dispatch_ctas must be in [1,8]");
+    g_dispatch_ctas.store(value);
+    return SB_OK;
+  }
+  return SB_E_UNSUPPORTED;
+}
+static int dispatch_ctas_per_sm() { return g_dispatch_ctas.load(std::memory_order_relaxed); }
+
 namespace {
 
 constexpr int kMaxRanks = 16;
@@ -218,7 +233,22 @@ __device__ __forceinline__ void dispatch_body(const uint4 *__restrict__ x, const
     }
     const uint4 *s = x + (size_t)(i / items_per_row) * vec_per_row;
     uint4 *dp = static_cast<uint4 *>(recv_rows.p[d]) + (size_t)row * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) dp[v] = __ldg(s + v);
+    // eight 16-byte loads in flight per lane, then the eight peer stores: a 4 KB row is
+    // one batch, so few warps keep the link busy and the GEMM that runs beside this
+    // kernel keeps its issue slots
+    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+      uint4 t[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int v = v0 + j * 32 + lane;
+        if (v < vec_per_row) t[j] = __ldg(s + v);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int v = v0 + j * 32 + lane;
+        if (v < vec_per_row) dp[v] = t[j];
+      }
+    }
     if (lane == 0) {
       static_cast<__nv_bfloat16 *>(recv_scale.p[d])[row] = item_scale[i];
       // return address of the row: sender rank and the sender's item index
@@ -595,7 +625,7 @@ int32_t sb_ep_dispatch(const void *x, const int32_t *item_expert, const void *it
   for (int i = 0; i < kMaxRanks; ++i) pm.p[i] = nullptr;
   if (peer_meta != nullptr && (rc = fill_peers(&pm, peer_meta, ep, "sb_ep_dispatch")) != SB_OK) return rc;
   int blocks = (n_items + 7) / 8;
-  const int max_blocks = sb_device_sm_count() * 8;
+  const int max_blocks = sb_device_sm_count() * dispatch_ctas_per_sm();
   if (blocks > max_blocks) blocks = max_blocks;
   ep_dispatch_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4 *>(x), item_expert, static_cast<const __nv_bfloat16 *>(item_scale),

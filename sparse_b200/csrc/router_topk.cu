@@ -105,6 +105,13 @@ __device__ void warp_softmax_topk(const float *lg, int E, int K, int renorm, int
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i)
     if (p[i] >= 0.f) p[i] = __fdiv_rn(p[i], s);
+  // A row with a NaN or an infinite logit has NaN probabilities.  torch.topk ranks
+  // NaN above every number (utils/eval_core.py:9591-9595 calls it); here NaN gets
+  // the key 3 for the selection, so that the indices written are always expert
+  // ids, and the weight written for it is NaN again.
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i)
+    if (p[i] != p[i]) p[i] = 3.f;
 
   float sel_v[kMaxK];
   int sel_i[kMaxK];
@@ -124,7 +131,7 @@ __device__ void warp_softmax_topk(const float *lg, int E, int K, int renorm, int
       int oi = __shfl_xor_sync(0xffffffffu, bi, off);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    sel_v[k] = bv; sel_i[k] = bi;
+    sel_v[k] = bv > 2.f ? __int_as_float(0x7fc00000) : bv; sel_i[k] = bi;
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i)
       if (lane + 32 * i == bi) p[i] = -1.f;

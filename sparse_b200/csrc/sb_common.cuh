@@ -108,6 +108,7 @@ int32_t launch_grouped_swiglu_pair(const void *rows, const int32_t *tile_table, 
                                    const unsigned long long *row_dst, cudaStream_t stream, int passes = 3,
                                    int stages = 0);
 int32_t set_gemm_tuning(const char *key, int value);
+int32_t set_ep_tuning(const char *key, int value);       // SB_E_UNSUPPORTED: not one of its keys
 int32_t launch_decode_experts(const void *x, const int32_t *item_of_slot, int items_per_row,
                               const int32_t *tile_table, const int32_t *slot_of_expert, const void *w13,
                               const void *w2, const void *row_scale, int H, int I, int n_slots, void *hbuf,

@@ -121,13 +121,21 @@ def grouped_swiglu(rows: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor,
 
 
 def combine(rows_out: torch.Tensor, slot_of_item: torch.Tensor, idx: torch.Tensor,
-            shared_out: Optional[torch.Tensor], tokens: int) -> torch.Tensor:
+            shared_out: Optional[torch.Tensor], tokens: int,
+            shared_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`shared_scale` [T] bf16: the shared expert's scalar gate, applied to `shared_out`'s
+    rows on the way (sb_combine_gated)."""
     h = rows_out.shape[1]
     k = idx.shape[1]
     out = torch.empty((tokens, h), dtype=torch.bfloat16, device=rows_out.device)
     with torch.cuda.device(rows_out.device):
-        check(lib.sb_combine(_ptr(rows_out), _ptr(slot_of_item), _ptr(idx), _ptr(shared_out), tokens,
-                             h, k, _ptr(out), _stream(rows_out)), "sb_combine")
+        if shared_scale is None:
+            check(lib.sb_combine(_ptr(rows_out), _ptr(slot_of_item), _ptr(idx), _ptr(shared_out), tokens,
+                                 h, k, _ptr(out), _stream(rows_out)), "sb_combine")
+        else:
+            check(lib.sb_combine_gated(_ptr(rows_out), _ptr(slot_of_item), _ptr(idx), _ptr(shared_out),
+                                       _ptr(shared_scale), tokens, h, k, _ptr(out), _stream(rows_out)),
+                  "sb_combine_gated")
     return out
 
 

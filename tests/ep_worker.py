@@ -213,6 +213,18 @@ def main():
             assert torch.equal(out, want_g[it % 2]), "graph-replayed EP rows differ on rank %d (pass %d)" % (rank, it)
         blk.use_graphs = False
         dist.barrier()
+        # the other step order (router beside the shared expert's gate/up pass instead
+        # of in front of it) gives the same rows
+        ep_layer = getattr(blk, "_ep", None) or getattr(blk, "ep_layer", None)
+        if ep_layer is not None and hasattr(ep_layer, "router_first"):
+            ep_layer.router_first = not ep_layer.router_first
+            for it in range(2):
+                out = blk.forward_device(xg[it]).clone()
+                torch.cuda.synchronize()
+                blk.check_status()
+                assert torch.equal(out, want_g[it]), "rows differ with the other router order on rank %d" % rank
+            ep_layer.router_first = not ep_layer.router_first
+            dist.barrier()
     offloaded_case(rank, world, dev)
     local_cache_case(rank, world, dev)
     print("EP_WORKER_OK rank %d" % rank, flush=True)

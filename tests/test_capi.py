@@ -45,6 +45,8 @@ def test_bad_arguments_are_rejected_with_a_message():
     assert rc == -1
     rc = lib.sb_combine(None, None, None, None, 4, 2048, 9, None, None)
     assert rc == -1 and b"sb_combine" in lib.sb_last_error_string()
+    assert lib.sb_combine_gated(None, None, None, None, None, 4, 2048, 9, None, None) == -1
+    assert lib.sb_combine_gated(None, None, None, None, None, 0, 2048, 4, None, None) == 0
     rc = lib.sb_grouped_swiglu(None, None, 0, None, None, None, None, 128, 2000, 1408, 1, None, None, None, None)
     assert rc == -4 and b"multiples of 64" in lib.sb_last_error_string()
     rc = lib.sb_permute(None, None, None, 8, 1, 2048, 300, None, 0, None, None, None, None, None, None, None)

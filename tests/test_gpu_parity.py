@@ -495,6 +495,35 @@ def test_combine_bit_exact(t, k, h, e):
     assert torch.equal(got.cpu(), want)
     got2 = ops.combine(rows.to(dev()), slot_of_item.to(torch.int32).to(dev()), idx.to(dev()), None, t)
     assert torch.equal(got2.cpu(), mo.combine_expert_outputs(parts, idx.long()))
+    # the shared expert's scalar gate applied on the way: bf16(shared * gate), then the add
+    gate = torch.rand(t).to(torch.bfloat16)
+    want3 = mo.combine_expert_outputs(parts, idx.long()) + (shared.float() * gate.float()[:, None]).to(torch.bfloat16)
+    got3 = ops.combine(rows.to(dev()), slot_of_item.to(torch.int32).to(dev()), idx.to(dev()),
+                       shared.to(dev()), t, shared_scale=gate.to(dev()))
+    assert torch.equal(got3.cpu(), want3)
+
+
+def test_gate_in_combine_equals_gate_in_the_down_pass():
+    """The shared expert's rows scaled by its GEMM's epilogue (row_scale) and then
+    added, against unscaled rows with the gate applied by sb_combine_gated: same bits."""
+    from sparse_b200 import ops
+    torch.manual_seed(3)
+    bf = torch.bfloat16
+    t, h, i, k, e = 300, 256, 192, 2, 8
+    d = dev()
+    w13 = (torch.randn(1, 2 * i, h, device=d) * 0.05).to(bf)
+    w2 = (torch.randn(1, h, i, device=d) * 0.05).to(bf)
+    x = torch.randn(t, h, device=d).to(bf)
+    gate = torch.rand(t, device=d).to(bf)
+    scaled = ops.grouped_swiglu(x, w13, w2, dense_rows=t, row_scale=gate)[0]
+    raw = ops.grouped_swiglu(x, w13, w2, dense_rows=t)[0]
+    idx = torch.stack([torch.randperm(e)[:k] for _ in range(t)]).to(torch.int32)
+    slot_of_item, _, _ = mo.expert_sorted_permutation(idx, e)
+    rows = torch.randn(t * k, h, device=d).to(bf)
+    soi = slot_of_item.to(torch.int32).to(d)
+    a = ops.combine(rows, soi, idx.to(d), scaled, t)
+    b = ops.combine(rows, soi, idx.to(d), raw, t, shared_scale=gate)
+    assert torch.equal(a, b)
 
 
 # ------------------------------------------------------------- whole layer ----
@@ -620,3 +649,24 @@ def test_empty_input():
     runner = LayerRunner(lw, 2, 16)
     out, idx, wts, logits = runner.forward(torch.empty((0, 256), dtype=torch.bfloat16, device=dev()))
     assert out.shape == (0, 256) and idx.shape == (0, 2)
+
+
+def test_topk_of_a_row_with_nan_or_inf_still_names_experts():
+    """A NaN or infinite logit makes the row's probabilities NaN; the indices written
+    must still be K distinct expert ids (the permutation and the GEMM index with
+    them), the weights are NaN as torch.topk's would be."""
+    from sparse_b200 import ops
+    torch.manual_seed(11)
+    t, e, k = 64, 60, 4
+    logits = torch.randn(t, e).to(torch.bfloat16)
+    logits[3, 7] = float("nan")
+    logits[9, :] = float("nan")
+    logits[20, 5] = float("inf")
+    idx, wts = ops.softmax_topk(logits.to(dev()), k)
+    idx = idx.cpu().long()
+    assert int(idx.min()) >= 0 and int(idx.max()) < e
+    assert all(len(set(row.tolist())) == k for row in idx)
+    clean = [r for r in range(t) if r not in (3, 9, 20)]
+    _, want_i = mo.softmax_topk(logits[clean], k, False, torch.bfloat16)
+    assert torch.equal(idx[clean], want_i)
+    assert bool(torch.isnan(wts.cpu().float()[[3, 9, 20]]).all())
