@@ -767,7 +767,7 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
                     const unsigned long long *row_dst, int n_stages, uint32_t stage_bytes, cudaStream_t stream) {
   const int n_wtiles = (w_rows + kTileW - 1) / kTileW;
   const int dense_chunk = tile_table == nullptr ? dense_chunk_rows(dense_rows, n_wtiles, grid / 2) : kMaxN;
-  const int probe_light = 16;
+  const int light_rows_per_cta = 16;      // tiles with at most this many tokens per CTA take two K steps per 36 KB stage
   auto kern = pair_gemm_kernel<MODE>;
   const int mode_now = sched_mode();
   const bool tail = row_dst != nullptr || (tile_table != nullptr && mode_now != 0);
@@ -775,7 +775,7 @@ int32_t launch_pass(const CUtensorMap &tm_w, const CUtensorMap *tm_x, const int3
                                                         slot_of_expert,
                                                         static_cast<const __nv_bfloat16 *>(row_scale),
                                                         static_cast<__nv_bfloat16 *>(out), ld_out, w_rows, num_kb,
-                                                        n_slots, status, skip_rows_upto, dense_chunk, probe_light,
+                                                        n_slots, status, skip_rows_upto, dense_chunk, light_rows_per_cta,
                                                         row_dst, n_stages, mode_now,
                                                         g_dense_group.load(std::memory_order_relaxed), stage_bytes);
   SB_LAUNCH_CHECK();
