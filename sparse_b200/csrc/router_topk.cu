@@ -257,6 +257,46 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
         if (lane < G && wp[r] != nullptr)
           cur[r][v] = __ldg(reinterpret_cast<const uint4 *>(wp[r] + (size_t)lane * 8) + v);
       }
+    // Full token tile and a hidden size of whole 256-element steps (the usual
+    // case): the same arithmetic without the per-token and per-row guards.  Rows
+    // past the last one read row 0's weights; their sums are never stored.
+    if (tb_eff == TB && (G & 31) == 0) {
+      const IN *wq[RW];
+#pragma unroll
+      for (int r = 0; r < RW; ++r) wq[r] = wp[r] != nullptr ? wp[r] : wg;
+#pragma unroll
+      for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int v = 0; v < kVecPerGroup; ++v)
+          cur[r][v] = __ldg(reinterpret_cast<const uint4 *>(wq[r] + (size_t)lane * 8) + v);
+#pragma unroll 1
+      for (int j = 0; j < steps; ++j) {
+        const int g = j * 32 + lane;
+        if (j + 1 < steps) {
+#pragma unroll
+          for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int v = 0; v < kVecPerGroup; ++v)
+              nxt[r][v] = __ldg(reinterpret_cast<const uint4 *>(wq[r] + (size_t)(g + 32) * 8) + v);
+        }
+        Pair4<IN> w[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) w[r].load(&cur[r][0]);
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+          Pair4<IN> xv;
+          xv.load(sx + ((size_t)t * G + g) * kVecPerGroup);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int r = 0; r < RW; ++r) acc[t][r].fma(xv, w[r], i);
+        }
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+          for (int v = 0; v < kVecPerGroup; ++v) cur[r][v] = nxt[r][v];
+      }
+    } else
     for (int j = 0; j < steps; ++j) {
       const int g = j * 32 + lane;
       const int gn = g + 32;
