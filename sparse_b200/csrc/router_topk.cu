@@ -80,6 +80,26 @@ __device__ __forceinline__ float butterfly_max(float v) {
   return v;
 }
 
+// Sums of 32 values over the 32 lanes at once: lane i returns the warp-wide sum of
+// v[i].  Each step halves the values a lane still carries (it keeps the half that
+// its lane-id bit selects and hands the other half to its partner), so this takes
+// 31 shuffles instead of 32 x 5.  The additions pair the same lanes at the same
+// offsets (16, 8, 4, 2, 1) as butterfly_sum, and fp32 addition is commutative:
+// the result has the bits butterfly_sum gives for that value on every lane.
+__device__ __forceinline__ float warp_sum_each(float (&v)[32], int lane) {
+#pragma unroll
+  for (int half = 16; half >= 1; half >>= 1) {
+    const bool upper = (lane & half) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float keep = upper ? v[i + half] : v[i];
+      const float send = upper ? v[i] : v[i + half];
+      v[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, half));
+    }
+  }
+  return v[0];
+}
+
 // One warp: softmax over E model-dtype logits (given as fp32 values) and top-k.
 // `lg` points at this token's E logits in shared memory.
 template <typename IN>
@@ -260,7 +280,7 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
     // Full token tile and a hidden size of whole 256-element steps (the usual
     // case): the same arithmetic without the per-token and per-row guards.  Rows
     // past the last one read row 0's weights; their sums are never stored.
-    if (tb_eff == TB && (G & 31) == 0) {
+    if (TB < 8 && tb_eff == TB && (G & 31) == 0) {      // (the 8-token tile has no registers to spare for a second loop)
       const IN *wq[RW];
 #pragma unroll
       for (int r = 0; r < RW; ++r) wq[r] = wp[r] != nullptr ? wp[r] : wg;
@@ -329,17 +349,34 @@ router_kernel(const IN *__restrict__ x, const IN *__restrict__ wg, const float *
 #pragma unroll
         for (int v = 0; v < kVecPerGroup; ++v) cur[r][v] = nxt[r][v];
     }
+    if (TB * RW < 32) {                 // (a full 32 would need every register the loop above holds)
+      // lane t*RW + r ends up with the logit of (token t, row r of this group)
+      float part[32];
 #pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      if (t < tb_eff) {
+      for (int i = 0; i < 32; ++i) part[i] = 0.f;
 #pragma unroll
-        for (int r = 0; r < RW; ++r) {
-          const int row = grp * RW + r;
-          float sum = butterfly_sum(acc[t][r].lane_sum());
-          if (lane == 0 && row < NR) {
-            if (row < E && bias != nullptr) sum = __fadd_rn(sum, bias[row]);
-            // the shared gate's logit (row E) is always a model-dtype linear output
-            slog[t * ldl + row] = (fp32_logits && row < E) ? sum : Load8<IN>::round_model(sum);
+      for (int t = 0; t < TB; ++t)
+#pragma unroll
+        for (int r = 0; r < RW; ++r) part[t * RW + r] = acc[t][r].lane_sum();
+      float sum = warp_sum_each(part, lane);
+      const int t = lane / RW, row = grp * RW + lane % RW;
+      if (t < tb_eff && row < NR) {
+        if (row < E && bias != nullptr) sum = __fadd_rn(sum, bias[row]);
+        // the shared gate's logit (row E) is always a model-dtype linear output
+        slog[t * ldl + row] = (fp32_logits && row < E) ? sum : Load8<IN>::round_model(sum);
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < TB; ++t) {
+        if (t < tb_eff) {
+#pragma unroll
+          for (int r = 0; r < RW; ++r) {
+            const int row = grp * RW + r;
+            float sum = butterfly_sum(acc[t][r].lane_sum());
+            if (lane == 0 && row < NR) {
+              if (row < E && bias != nullptr) sum = __fadd_rn(sum, bias[row]);
+              slog[t * ldl + row] = (fp32_logits && row < E) ? sum : Load8<IN>::round_model(sum);
+            }
           }
         }
       }
