@@ -4,6 +4,8 @@ import ctypes as C
 import os
 import re
 
+import pytest
+
 from conftest import ROOT
 
 
@@ -77,6 +79,20 @@ def test_tuning_knob_argument_checks():
     lib = _lib.lib
     assert lib.sb_set_tuning(b"sched", 0) == 0 and lib.sb_set_tuning(b"dense_group", 1) == 0
     assert lib.sb_set_tuning(b"router_overlap", 1) == 0
-    for key, bad in ((b"sched", -1), (b"sched", 3), (b"dense_group", 0), (b"dense_group", 65), (b"router_overlap", 2)):
+    assert lib.sb_set_tuning(b"kslabs", 2) == 0 and lib.sb_set_tuning(b"dispatch_ctas", 1) == 0
+    for key, bad in ((b"sched", -1), (b"sched", 3), (b"dense_group", 0), (b"dense_group", 65), (b"router_overlap", 2),
+                     (b"kslabs", 0), (b"kslabs", 3), (b"dispatch_ctas", 0), (b"dispatch_ctas", 9)):
         assert lib.sb_set_tuning(key, bad) != 0
     assert lib.sb_set_tuning(b"unknown", 0) != 0 and lib.sb_set_tuning(None, 0) != 0
+
+
+def test_tuning_from_the_environment(monkeypatch):
+    """SPARSE_B200_TUNING="key=value,..." is applied through sb_set_tuning; a bad entry raises."""
+    from sparse_b200 import _lib
+    monkeypatch.setenv("SPARSE_B200_TUNING", "kslabs=1, dispatch_ctas=4")
+    _lib.apply_tuning_from_env()
+    monkeypatch.setenv("SPARSE_B200_TUNING", "kslabs=7")
+    with pytest.raises(ValueError):
+        _lib.apply_tuning_from_env()
+    monkeypatch.setenv("SPARSE_B200_TUNING", "kslabs=2,dispatch_ctas=1")
+    _lib.apply_tuning_from_env()
